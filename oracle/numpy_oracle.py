@@ -1,0 +1,314 @@
+"""CPU oracle for the Handler hot path -- TEST INFRASTRUCTURE, NOT PRODUCT CODE.
+
+A numpy restatement of what the reference's CPU backend
+(``brainstorm/handlers/numpy_handler.py``, class ``NumpyHandler``) computes for
+every operation of the ``Handler`` API (``brainstorm/handlers/base_handler.py``)
+that the B200 backend implements, plus the per-timestep LSTM gate arithmetic of
+``brainstorm/layers/lstm_layer.py``.  Only the tests, the smoke check and the
+``cpu_baseline`` / ``--impl reference`` legs of the benchmark may import it; the
+product package never does.
+
+Parity pin: ``tests/golden/*.npz`` were produced by running the *real*
+``NumpyHandler`` (and the real ``LstmLayerImpl`` on it) on seeded inputs
+(``tests/golden/make_golden.py``); ``tests/test_oracle_golden.py`` requires this
+module to reproduce every stored output bit for bit.
+
+Conventions follow the reference: every op writes into a pre-allocated ``out``
+and returns ``None``; ``out`` may alias an input; shapes are not checked.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+
+class OracleHandler(object):
+    """Same method names, argument order and semantics as ``NumpyHandler``."""
+
+    array_type = np.ndarray
+
+    def __init__(self, dtype=np.float32, seed=None):
+        self.dtype = np.dtype(dtype).type
+        self.rnd = np.random.RandomState(seed)
+
+    # ---- allocation / transfer: numpy_handler.py:36-65 -------------------
+    def allocate(self, shape):
+        # numpy_handler.py:36 -- zero-filled, although the API says "arbitrary"
+        return np.zeros(shape, dtype=self.dtype)
+
+    def zeros(self, shape):                         # numpy_handler.py:42
+        return np.zeros(shape, dtype=self.dtype)
+
+    def ones(self, shape):                          # numpy_handler.py:39
+        return np.ones(shape, dtype=self.dtype)
+
+    def create_from_numpy(self, arr):               # numpy_handler.py:54
+        return np.array(arr, dtype=self.dtype)
+
+    def set_from_numpy(self, mem, arr):             # numpy_handler.py:64
+        mem[...] = np.asarray(arr).astype(self.dtype)
+
+    def get_numpy_copy(self, mem):                  # numpy_handler.py:60
+        return np.array(mem, copy=True)
+
+    def fill(self, mem, val):                       # numpy_handler.py:57
+        mem[...] = val
+
+    def copy_to(self, src, dest):                   # numpy_handler.py:47 (src, dest)
+        np.copyto(dest, src, casting='same_kind')
+
+    def is_fully_finite(self, a):                   # numpy_handler.py:69
+        return bool(np.isfinite(a).all())
+
+    # ---- tensor (.) tensor: numpy_handler.py:86,264,245,190,233 ----------
+    def add_tt(self, a, b, out):
+        np.add(a, b, out=out)
+
+    def subtract_tt(self, a, b, out):
+        np.subtract(a, b, out=out)
+
+    def mult_tt(self, a, b, out):
+        np.multiply(a, b, out=out)
+
+    def divide_tt(self, a, b, out):
+        np.divide(a, b, out=out)
+
+    def mult_add_tt(self, a, b, out):
+        # numpy_handler.py:233 -- product rounded, then sum rounded (no FMA)
+        prod = np.multiply(a, b)
+        np.add(out, prod, out=out)
+
+    def modulo_tt(self, a, b, out):                 # numpy_handler.py:227
+        np.fmod(a, b, out=out)
+
+    # ---- matrix (.) broadcast vector: numpy_handler.py:80,261,236,187,239 -
+    def add_mv(self, m, v, out):
+        np.add(m, v, out=out)
+
+    def subtract_mv(self, m, v, out):
+        np.subtract(m, v, out=out)
+
+    def mult_mv(self, m, v, out):
+        np.multiply(m, v, out=out)
+
+    def divide_mv(self, m, v, out):
+        np.divide(m, v, out=out)
+
+    def mult_add_mv(self, m, v, out):
+        prod = np.multiply(m, v)
+        np.add(out, prod, out=out)
+
+    def broadcast_t(self, a, axis, out):            # numpy_handler.py:103
+        out[...] = a
+
+    # ---- scalar (.) tensor: numpy_handler.py:83,242,230 ------------------
+    def add_st(self, s, t, out):
+        np.add(t, s, out=out)
+
+    def mult_st(self, s, t, out):
+        np.multiply(s, t, out=out)
+
+    def mult_add_st(self, s, t, out):
+        prod = np.multiply(s, t)
+        np.add(out, prod, out=out)
+
+    # ---- unary: numpy_handler.py:74,248,258,207,107 ----------------------
+    def abs_t(self, a, out):
+        np.absolute(a, out=out)
+
+    def sign_t(self, a, out):
+        np.sign(a, out=out)
+
+    def sqrt_t(self, a, out):
+        np.sqrt(a, out=out)
+
+    def log_t(self, a, out):
+        np.log(a, out=out)
+
+    def clip_t(self, a, a_min, a_max, out):
+        np.clip(a, a_min, a_max, out=out)
+
+    # ---- predicated ops: numpy_handler.py:173,196,77 ---------------------
+    def copy_to_if(self, src, dest, cond):
+        sel = cond != 0
+        dest[sel] = src[sel]
+
+    def fill_if(self, mem, val, cond):
+        mem[cond != 0] = val
+
+    def add_into_if(self, a, out, cond):
+        sel = cond != 0
+        out[sel] += a[sel]
+
+    # ---- concat / split on the last axis: numpy_handler.py:221,251 -------
+    def merge_tt(self, a, b, out):
+        na = a.shape[-1]
+        o2 = out.reshape(-1, out.shape[-1])
+        o2[:, :na] = a.reshape(-1, na)
+        o2[:, na:] = b.reshape(-1, b.shape[-1])
+
+    def split_add_tt(self, x, out_a, out_b):
+        na = out_a.shape[-1]
+        x2 = x.reshape(-1, x.shape[-1])
+        oa = out_a.reshape(-1, na)
+        ob = out_b.reshape(-1, out_b.shape[-1])
+        oa += x2[:, :na]
+        ob += x2[:, na:]
+
+    # ---- reductions: numpy_handler.py:268,292 ----------------------------
+    def sum_t(self, a, axis, out):
+        keep = axis is not None and out.ndim == a.ndim
+        np.sum(a, axis=axis, out=out, keepdims=keep)
+
+    def softmax_m(self, m, out):
+        shifted = m - np.amax(m, axis=1, keepdims=True)
+        e = np.exp(shifted)
+        np.divide(e, np.sum(e, axis=1, keepdims=True), out=out)
+
+    # ---- label ops (bit-exact): numpy_handler.py:99,202 ------------------
+    def binarize_v(self, v, out):
+        labels = v.astype(np.int32).reshape(-1)
+        out[...] = 0
+        out[np.arange(out.shape[0]), labels] = 1
+
+    def index_m_by_v(self, m, v, out):
+        labels = v.astype(np.int32).reshape(-1)
+        out[:, 0] = m[np.arange(m.shape[0]), labels]
+
+    # ---- GEMM: numpy_handler.py:176,181 ----------------------------------
+    def dot_mm(self, a, b, out, transa=False, transb=False):
+        out[...] = np.dot(a.T if transa else a, b.T if transb else b)
+
+    def dot_add_mm(self, a, b, out, transa=False, transb=False):
+        out[...] += np.dot(a.T if transa else a, b.T if transb else b)
+
+    # ---- random: numpy_handler.py:193,199 (MT19937 RandomState) ----------
+    def fill_gaussian(self, mean, std, out):
+        out[...] = std * self.rnd.standard_normal(out.shape) + mean
+
+    def generate_probability_mask(self, mask, probability):
+        mask[...] = self.rnd.uniform(size=mask.shape) < probability
+
+    # ---- activations: numpy_handler.py:277-309 ---------------------------
+    def sigmoid(self, x, y):
+        # numpy_handler.py:283 uses two boolean-mask passes: 1/(1+exp(-x)) for
+        # x >= 0 and exp(x)/(1+exp(x)) for x < 0.  exp(-|x|) equals exp(-x) on
+        # the first branch and exp(x) on the second, so one pass gives the same
+        # bits without overflow (and without the mask indexing cost).
+        e = np.exp(-np.abs(x))
+        one = self.dtype(1)
+        y[...] = np.where(x >= 0, one / (one + e), e / (one + e))
+
+    def sigmoid_deriv(self, x, y, dy, dx):
+        dx[...] = dy * y * (self.dtype(1) - y)
+
+    def tanh(self, x, y):
+        np.tanh(x, out=y)
+
+    def tanh_deriv(self, x, y, dy, dx):
+        dx[...] = dy * (self.dtype(1) - y * y)
+
+    def rel(self, x, y):
+        # x * (x > 0): negatives become -0.0, NaN stays NaN
+        y[...] = x * (x > 0)
+
+    def rel_deriv(self, x, y, dy, dx):
+        dx[...] = dy * (y > 0)
+
+    def el(self, x, y):
+        # note >= at zero and exp(x) - 1 (not expm1), as numpy_handler.py:305
+        y[...] = x * (x >= 0) + (np.exp(x) - self.dtype(1)) * (x < 0)
+
+    def el_deriv(self, x, y, dy, dx):
+        dx[...] = dy * (y >= 0) + dy * (y + self.dtype(1)) * (y < 0)
+
+    def act(self, name, x, y):
+        """Dispatch like ``Handler.act_func`` (base_handler.py:57-63)."""
+        if name == 'linear':
+            self.copy_to(x, y)
+        else:
+            getattr(self, name)(x, y)
+
+    def act_deriv(self, name, x, y, dy, dx):
+        """Dispatch like ``Handler.act_func_deriv`` (base_handler.py:65-72)."""
+        if name == 'linear':
+            self.copy_to(dy, dx)
+        else:
+            getattr(self, name + '_deriv')(x, y, dy, dx)
+
+    # ---- fused LSTM timestep, restated from lstm_layer.py ----------------
+    def lstm_step_forward(self, Za, Ia, Fa, Oa, Ca_prev, bz, bi, bf, bo,
+                          pi, pf, po, Zb, Ib, Fb, Ob, Ca, Cb, y,
+                          activation='tanh'):
+        """Gate math of one timestep, lstm_layer.py:117-145 minus the four
+        recurrent GEMMs, which must already have been accumulated into the
+        pre-activations ``Za, Ia, Fa, Oa``.  All arrays are (B, H); biases and
+        peepholes are (1, H) or (H,).  Updates the pre-activations in place as
+        the reference does and writes ``Zb, Ib, Fb, Ob, Ca, Cb, y``."""
+        r = lambda p: p.reshape(1, -1)
+        self.add_mv(Za, r(bz), Za)                      # :118
+        self.act(activation, Za, Zb)                    # :119
+        self.mult_add_mv(Ca_prev, r(pi), Ia)            # :123
+        self.add_mv(Ia, r(bi), Ia)                      # :124
+        self.sigmoid(Ia, Ib)                            # :125
+        self.mult_add_mv(Ca_prev, r(pf), Fa)            # :129
+        self.add_mv(Fa, r(bf), Fa)                      # :130
+        self.sigmoid(Fa, Fb)                            # :131
+        self.mult_tt(Ib, Zb, Ca)                        # :134
+        self.mult_add_tt(Fb, Ca_prev, Ca)               # :135
+        self.mult_add_mv(Ca, r(po), Oa)                 # :139
+        self.add_mv(Oa, r(bo), Oa)                      # :140
+        self.sigmoid(Oa, Ob)                            # :141
+        self.act(activation, Ca, Cb)                    # :144
+        self.mult_tt(Ob, Cb, y)                         # :145
+
+    def lstm_step_backward(self, dy, dIa_next, dFa_next, dCa_next, Fb_next,
+                           pi, pf, po, Za, Zb, Ia, Ib, Fa, Fb, Oa, Ob, Ca, Cb,
+                           Ca_prev, dZa, dZb, dIa, dIb, dFa, dFb, dOa, dOb,
+                           dCa, dCb, activation='tanh'):
+        """Gate math of one backward timestep, lstm_layer.py:179-205.  ``dy``
+        already holds the output deltas plus the four recurrent GEMM
+        contributions (:173-177).  ``dCa`` is accumulated into (it starts at
+        zero, :168); everything else is overwritten."""
+        r = lambda p: p.reshape(1, -1)
+        self.mult_add_mv(dIa_next, r(pi), dCa)          # :180
+        self.mult_add_mv(dFa_next, r(pf), dCa)          # :181
+        self.mult_tt(dy, Cb, dOb)                       # :184
+        self.sigmoid_deriv(Oa, Ob, dOb, dOa)            # :185
+        self.mult_add_mv(dOa, r(po), dCa)               # :187
+        self.mult_tt(dy, Ob, dCb)                       # :190
+        self.act_deriv(activation, Ca, Cb, dCb, dCb)    # :191
+        self.add_tt(dCa, dCb, dCa)                      # :192
+        self.mult_add_tt(dCa_next, Fb_next, dCa)        # :193
+        self.mult_tt(dCa, Ca_prev, dFb)                 # :196
+        self.sigmoid_deriv(Fa, Fb, dFb, dFa)            # :197
+        self.mult_tt(dCa, Zb, dIb)                      # :200
+        self.sigmoid_deriv(Ia, Ib, dIb, dIa)            # :201
+        self.mult_tt(dCa, Ib, dZb)                      # :204
+        self.act_deriv(activation, Za, Zb, dZb, dZa)    # :205
+
+
+# --------------------------------------------------------------------------
+# Seeded synthetic inputs of the benchmark configurations (shared by the
+# parity tests and the CPU-baseline leg of the benchmark so that both sides see
+# the same data).
+# --------------------------------------------------------------------------
+def op_suite_inputs(rows, cols, seed):
+    """Inputs of the handler op suite: fp32 (rows, cols) uniform[-4, 4]
+    operands, a (1, cols) row vector, a (rows, 1) column vector, divisors
+    uniform[0.5, 4] with a random sign and int labels uniform in [0, cols)."""
+    rs = np.random.RandomState(seed)
+    f32 = np.float32
+
+    def u(shape, lo=-4.0, hi=4.0):
+        return (rs.random_sample(shape).astype(f32) * f32(hi - lo) + f32(lo))
+
+    d = {}
+    d['a'] = u((rows, cols))
+    d['b'] = u((rows, cols))
+    d['dy'] = u((rows, cols))
+    d['row'] = u((1, cols))
+    d['col'] = u((rows, 1))
+    sign = np.where(rs.random_sample((rows, cols)) < 0.5, f32(-1), f32(1))
+    d['div'] = (u((rows, cols), 0.5, 4.0) * sign).astype(f32)
+    d['labels'] = rs.randint(0, cols, size=(rows, 1)).astype(np.int32)
+    return d
