@@ -1,0 +1,96 @@
+// Shared declarations of the B200 handler library: status codes, the error
+// slot behind b200_last_error(), the library's current stream and a few device
+// helpers.  Everything here is internal; the public C-ABI is
+// include/b200_handler.h.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define B200_OK 0
+#define B200_ERR_CUDA 1
+#define B200_ERR_ARG 2
+#define B200_ERR_NCCL 3
+#define B200_ERR_DEVICE_FLAG 4
+#define B200_ERR_UNSUPPORTED 5
+
+#define B200_API extern "C" __attribute__((visibility("default")))
+
+namespace b200 {
+
+// ---- error slot ---------------------------------------------------------
+int set_error(int code, const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what, const char* file, int line);
+
+#define B200_CUDA(call)                                                        \
+  do {                                                                         \
+    cudaError_t e__ = (call);                                                  \
+    if (e__ != cudaSuccess) return b200::cuda_fail(e__, #call, __FILE__, __LINE__); \
+  } while (0)
+
+#define B200_REQUIRE(cond, ...)                                                \
+  do {                                                                         \
+    if (!(cond)) return b200::set_error(B200_ERR_ARG, __VA_ARGS__);            \
+  } while (0)
+
+// Checks the launch that has just been issued (asynchronous errors surface at
+// the next synchronising call).
+#define B200_LAUNCH_CHECK() B200_CUDA(cudaGetLastError())
+
+// ---- per-process state ----------------------------------------------------
+struct State {
+  bool ready = false;
+  int device = -1;
+  int sm_count = 148;
+  cudaStream_t stream = nullptr;
+  // tuning knobs (b200_set_tuning)
+  int ew_blocks_per_sm = 32;
+  int ew_threads = 1024;
+  int gemm_path = 0;  // 0 = auto, 1 = force SIMT, 2 = force tensor-core
+};
+State& state();
+int require_ready();
+
+static inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// ---- device helpers -------------------------------------------------------
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a thread block in a fixed order (lane tree, then warp 0 over the warp
+// partials): the same inputs always give the same bits.  `smem` holds >= 32
+// floats.  The result is valid in every thread.
+__device__ __forceinline__ float block_sum(float v, float* smem) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) smem[warp] = v;
+  __syncthreads();
+  float r = (lane < nwarps) ? smem[lane] : 0.f;
+  r = warp_sum(r);
+  return r;
+}
+__device__ __forceinline__ float block_max(float v, float* smem) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) smem[warp] = v;
+  __syncthreads();
+  float r = (lane < nwarps) ? smem[lane] : -INFINITY;
+  r = warp_max(r);
+  return r;
+}
+
+}  // namespace b200

@@ -1,0 +1,428 @@
+// Reductions of the B200 handler: sum_t over axis 0 / 1 / all, row softmax and the
+// finite check.  All HBM-bandwidth bound (every input byte is read once).
+//
+// Sums are deterministic two-pass trees: pass 1 writes one partial per block (or
+// per row-chunk and column) into caller-provided scratch in a fixed order, pass 2
+// adds the partials in a fixed order.  No floating-point atomics anywhere, so the
+// same input always gives the same bits.
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr int RED_THREADS = 256;
+constexpr int RED_MAX_PARTIALS = 4096;  // upper bound of pass-1 blocks / row chunks
+
+// ---- sum over everything ------------------------------------------------------------
+// Block b sums elements [b*chunk, min(n, (b+1)*chunk)); chunk is a multiple of 4.
+template <bool VEC>
+__global__ void __launch_bounds__(RED_THREADS)
+sum_all_pass1(const float* a, int64_t n, int64_t chunk, float* partial) {
+  __shared__ float smem[32];
+  const int64_t lo = (int64_t)blockIdx.x * chunk;
+  int64_t hi = lo + chunk;
+  if (hi > n) hi = n;
+  float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+  if (VEC) {
+    const int64_t nv = (hi - lo) >> 2;
+    const float4* p = reinterpret_cast<const float4*>(a + lo);
+    int64_t i = threadIdx.x;
+    for (; i + 3 * RED_THREADS < nv; i += 4 * RED_THREADS) {
+      const float4 v0 = __ldcs(p + i), v1 = __ldcs(p + i + RED_THREADS),
+                   v2 = __ldcs(p + i + 2 * RED_THREADS), v3 = __ldcs(p + i + 3 * RED_THREADS);
+      acc0 += (v0.x + v0.y) + (v0.z + v0.w);
+      acc1 += (v1.x + v1.y) + (v1.z + v1.w);
+      acc2 += (v2.x + v2.y) + (v2.z + v2.w);
+      acc3 += (v3.x + v3.y) + (v3.z + v3.w);
+    }
+    for (; i < nv; i += RED_THREADS) {
+      const float4 v0 = __ldcs(p + i);
+      acc0 += (v0.x + v0.y) + (v0.z + v0.w);
+    }
+    for (int64_t j = lo + (nv << 2) + threadIdx.x; j < hi; j += RED_THREADS) acc1 += a[j];
+  } else {
+    int64_t i = lo + threadIdx.x;
+    for (; i + 3 * RED_THREADS < hi; i += 4 * RED_THREADS) {
+      acc0 += a[i];
+      acc1 += a[i + RED_THREADS];
+      acc2 += a[i + 2 * RED_THREADS];
+      acc3 += a[i + 3 * RED_THREADS];
+    }
+    for (; i < hi; i += RED_THREADS) acc0 += a[i];
+  }
+  const float s = block_sum((acc0 + acc1) + (acc2 + acc3), smem);
+  if (threadIdx.x == 0) partial[blockIdx.x] = s;
+}
+
+// out[0] = sum of partial[0..count) in a fixed order (one block).
+__global__ void __launch_bounds__(RED_THREADS)
+sum_all_pass2(const float* partial, int count, float* out) {
+  __shared__ float smem[32];
+  float acc = 0.f;
+  for (int i = threadIdx.x; i < count; i += RED_THREADS) acc += partial[i];
+  const float s = block_sum(acc, smem);
+  if (threadIdx.x == 0) out[0] = s;
+}
+
+// ---- sum over axis 0 (column sums) ----------------------------------------------------
+// Block = 32 x 8 threads.  VEC: a thread owns 4 adjacent columns (block covers
+// 128 columns), else 1 column (block covers 32).  blockIdx.y selects a chunk of
+// rows; the block's result goes to dst[blockIdx.y * cols + c].
+template <bool VEC>
+__global__ void __launch_bounds__(256)
+sum_axis0_pass1(const float* a, int64_t rows, int64_t cols, int64_t ld, int64_t rows_per_chunk,
+                float* dst) {
+  constexpr int W = VEC ? 4 : 1;
+  __shared__ float smem[8][32 * W + 1];
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const int64_t c = ((int64_t)blockIdx.x * 32 + tx) * W;
+  const int64_t r_lo = (int64_t)blockIdx.y * rows_per_chunk;
+  int64_t r_hi = r_lo + rows_per_chunk;
+  if (r_hi > rows) r_hi = rows;
+  float acc[4][W];
+#pragma unroll
+  for (int u = 0; u < 4; ++u)
+#pragma unroll
+    for (int w = 0; w < W; ++w) acc[u][w] = 0.f;
+  if (c < cols) {
+    int64_t r = r_lo + ty;
+    for (; r + 24 < r_hi; r += 32) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float* p = a + (r + 8 * u) * ld + c;
+        if (VEC) {
+          const float4 v = __ldcs(reinterpret_cast<const float4*>(p));
+          acc[u][0] += v.x; acc[u][1 % W] += v.y; acc[u][2 % W] += v.z; acc[u][3 % W] += v.w;
+        } else {
+          acc[u][0] += __ldcs(p);
+        }
+      }
+    }
+    for (; r < r_hi; r += 8) {
+      const float* p = a + r * ld + c;
+      if (VEC) {
+        const float4 v = __ldcs(reinterpret_cast<const float4*>(p));
+        acc[0][0] += v.x; acc[0][1 % W] += v.y; acc[0][2 % W] += v.z; acc[0][3 % W] += v.w;
+      } else {
+        acc[0][0] += __ldcs(p);
+      }
+    }
+  }
+#pragma unroll
+  for (int w = 0; w < W; ++w)
+    smem[ty][tx * W + w] = (acc[0][w] + acc[1][w]) + (acc[2][w] + acc[3][w]);
+  __syncthreads();
+  // 32*W columns, summed over the 8 row lanes in a fixed order
+  for (int j = ty * 32 + tx; j < 32 * W; j += 256) {
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) s += smem[k][j];
+    const int64_t cc = (int64_t)blockIdx.x * 32 * W + j;
+    if (cc < cols) dst[(int64_t)blockIdx.y * cols + cc] = s;
+  }
+}
+
+// out[c] = sum over chunks of partial[chunk * cols + c], fixed order
+__global__ void __launch_bounds__(256)
+sum_axis0_pass2(const float* partial, int chunks, int64_t cols, float* out) {
+  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float s0 = 0.f, s1 = 0.f;
+  int k = 0;
+  for (; k + 1 < chunks; k += 2) {
+    s0 += partial[(int64_t)k * cols + c];
+    s1 += partial[(int64_t)(k + 1) * cols + c];
+  }
+  if (k < chunks) s0 += partial[(int64_t)k * cols + c];
+  out[c] = s0 + s1;
+}
+
+// ---- sum over axis 1 (row sums): one warp per row --------------------------------------
+template <bool VEC>
+__global__ void __launch_bounds__(256)
+sum_axis1_kernel(const float* a, int64_t rows, int64_t cols, int64_t ld, float* out) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const float* p = a + row * ld;
+  float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+  if (VEC) {
+    const int64_t nv = cols >> 2;
+    const float4* q = reinterpret_cast<const float4*>(p);
+    int64_t i = lane;
+    for (; i + 96 < nv; i += 128) {
+      const float4 v0 = __ldcs(q + i), v1 = __ldcs(q + i + 32), v2 = __ldcs(q + i + 64),
+                   v3 = __ldcs(q + i + 96);
+      acc0 += (v0.x + v0.y) + (v0.z + v0.w);
+      acc1 += (v1.x + v1.y) + (v1.z + v1.w);
+      acc2 += (v2.x + v2.y) + (v2.z + v2.w);
+      acc3 += (v3.x + v3.y) + (v3.z + v3.w);
+    }
+    for (; i < nv; i += 32) {
+      const float4 v0 = __ldcs(q + i);
+      acc0 += (v0.x + v0.y) + (v0.z + v0.w);
+    }
+  } else {
+    int64_t i = lane;
+    for (; i + 96 < cols; i += 128) {
+      acc0 += p[i]; acc1 += p[i + 32]; acc2 += p[i + 64]; acc3 += p[i + 96];
+    }
+    for (; i < cols; i += 32) acc0 += p[i];
+  }
+  const float s = warp_sum((acc0 + acc1) + (acc2 + acc3));
+  if (lane == 0) out[row] = s;
+}
+
+// ---- softmax over rows ------------------------------------------------------------------
+// The row lives in registers between the three phases (max, exp+sum, divide), so
+// the matrix is read once and written once.  G threads cooperate on a row
+// (G = 32: one warp per row; G = 256: one block per row); each holds VPT values.
+template <int G, int VPT, bool VEC>
+__global__ void __launch_bounds__(256)
+softmax_rows_kernel(const float* m, float* out, int64_t rows, int cols, int64_t ldm, int64_t ldo) {
+  __shared__ float smem[32];
+  constexpr int ROWS_PER_BLOCK = 256 / G;
+  const int g = threadIdx.x % G;
+  int64_t row = (int64_t)blockIdx.x * ROWS_PER_BLOCK + threadIdx.x / G;
+  const bool active = row < rows;
+  if (!active) {
+    if (G == 32) return;  // warps are independent
+    row = rows - 1;       // G == 256: whole block shares a row, never reached
+  }
+  const float* p = m + row * ldm;
+  float x[VPT];
+  float mx = -INFINITY;
+  if (VEC) {
+#pragma unroll
+    for (int k = 0; k < VPT / 4; ++k) {
+      const int c = (g + k * G) * 4;
+      float4 v = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+      if (c < cols) v = *reinterpret_cast<const float4*>(p + c);
+      x[4 * k] = v.x; x[4 * k + 1] = v.y; x[4 * k + 2] = v.z; x[4 * k + 3] = v.w;
+      mx = fmaxf(mx, fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int c = g + k * G;
+      x[k] = (c < cols) ? p[c] : -INFINITY;
+      mx = fmaxf(mx, x[k]);
+    }
+  }
+  mx = (G == 32) ? warp_max(mx) : block_max(mx, smem);
+  float sum = 0.f;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    x[k] = expf(x[k] - mx);  // padding: exp(-inf) = 0
+    sum += x[k];
+  }
+  sum = (G == 32) ? warp_sum(sum) : block_sum(sum, smem);
+  float* o = out + row * ldo;
+  if (VEC) {
+#pragma unroll
+    for (int k = 0; k < VPT / 4; ++k) {
+      const int c = (g + k * G) * 4;
+      if (c < cols)
+        *reinterpret_cast<float4*>(o + c) =
+            make_float4(__fdiv_rn(x[4 * k], sum), __fdiv_rn(x[4 * k + 1], sum),
+                        __fdiv_rn(x[4 * k + 2], sum), __fdiv_rn(x[4 * k + 3], sum));
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int c = g + k * G;
+      if (c < cols) o[c] = __fdiv_rn(x[k], sum);
+    }
+  }
+}
+
+// Rows too long for registers: one block per row, three passes over the row
+// (which stays in L2 between them).
+__global__ void __launch_bounds__(256)
+softmax_long_rows_kernel(const float* m, float* out, int64_t cols, int64_t ldm, int64_t ldo) {
+  __shared__ float smem[32];
+  const float* p = m + (int64_t)blockIdx.x * ldm;
+  float* o = out + (int64_t)blockIdx.x * ldo;
+  float mx = -INFINITY;
+  for (int64_t c = threadIdx.x; c < cols; c += 256) mx = fmaxf(mx, p[c]);
+  mx = block_max(mx, smem);
+  float sum = 0.f;
+  for (int64_t c = threadIdx.x; c < cols; c += 256) sum += expf(p[c] - mx);
+  sum = block_sum(sum, smem);
+  for (int64_t c = threadIdx.x; c < cols; c += 256) o[c] = __fdiv_rn(expf(p[c] - mx), sum);
+}
+
+// ---- finite check --------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+nonfinite_kernel(const float* a, int64_t rows, int64_t cols, int64_t ld, int* flag) {
+  const int64_t n = rows * cols;
+  int bad = 0;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / cols, c = i - r * cols;
+    const float v = a[r * ld + c];
+    bad |= !isfinite(v);
+  }
+  if (__syncthreads_or(bad) && threadIdx.x == 0) atomicOr(flag, 1);
+}
+
+static int axis0_plan(int64_t rows, int64_t cols, bool vec, int64_t* rows_per_chunk) {
+  const State& s = state();
+  const int64_t gx = ceil_div(cols, vec ? 128 : 32);
+  int64_t chunks = ceil_div((int64_t)s.sm_count * 8, gx);
+  const int64_t max_chunks = ceil_div(rows, 64);  // at least 64 rows per chunk
+  if (chunks > max_chunks) chunks = max_chunks;
+  if (chunks > RED_MAX_PARTIALS) chunks = RED_MAX_PARTIALS;
+  if (chunks < 1) chunks = 1;
+  *rows_per_chunk = ceil_div(rows, chunks);
+  return (int)ceil_div(rows, *rows_per_chunk);
+}
+
+static int all_plan(int64_t n, int64_t* chunk) {
+  const State& s = state();
+  int64_t blocks = ceil_div(n, (int64_t)RED_THREADS * 16);
+  const int64_t cap = (int64_t)s.sm_count * 8;
+  if (blocks > cap) blocks = cap;
+  if (blocks > RED_MAX_PARTIALS) blocks = RED_MAX_PARTIALS;
+  if (blocks < 1) blocks = 1;
+  int64_t c = ceil_div(n, blocks);
+  c = (c + 3) & ~(int64_t)3;
+  *chunk = c;
+  return (int)ceil_div(n, c);
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// Scratch floats that b200_sum_t needs for these extents (0: none).
+B200_API int64_t b200_sum_t_scratch_floats(int64_t rows, int64_t cols, int64_t ld, int axis) {
+  if (rows <= 0 || cols <= 0) return 0;
+  if (axis == 1) return 0;
+  if (axis == 0) {
+    const bool vec = (cols % 4 == 0) && (ld % 4 == 0);
+    int64_t rpc;
+    const int chunks = axis0_plan(rows, cols, vec, &rpc);
+    return chunks > 1 ? (int64_t)chunks * cols : 0;
+  }
+  // all: non-contiguous input goes through row sums first
+  if (rows > 1 && ld != cols) return rows + RED_MAX_PARTIALS;
+  return RED_MAX_PARTIALS;
+}
+
+static int sum_all_contiguous(const float* a, int64_t n, float* out, float* scratch) {
+  const State& s = state();
+  int64_t chunk;
+  const int blocks = all_plan(n, &chunk);
+  float* dst = blocks > 1 ? scratch : out;
+  if (aligned16(a))
+    sum_all_pass1<true><<<blocks, RED_THREADS, 0, s.stream>>>(a, n, chunk, dst);
+  else
+    sum_all_pass1<false><<<blocks, RED_THREADS, 0, s.stream>>>(a, n, chunk, dst);
+  B200_LAUNCH_CHECK();
+  if (blocks > 1) {
+    sum_all_pass2<<<1, RED_THREADS, 0, s.stream>>>(scratch, blocks, out);
+    B200_LAUNCH_CHECK();
+  }
+  return B200_OK;
+}
+
+// axis: 0 -> out[c] = sum_r a[r, c]; 1 -> out[r] = sum_c a[r, c]; -1 -> out[0] = sum of all.
+B200_API int b200_sum_t(const float* a, int64_t rows, int64_t cols, int64_t ld, int axis, float* out,
+                        float* scratch, int64_t scratch_floats) {
+  if (int rc = require_ready()) return rc;
+  B200_REQUIRE(rows >= 0 && cols >= 0 && out != nullptr, "bad extent or NULL out");
+  B200_REQUIRE(axis == 0 || axis == 1 || axis == -1, "axis must be 0, 1 or -1 (all)");
+  const State& s = state();
+  if (rows * cols == 0) {  // empty sum = 0 for every output element
+    const int64_t nout = axis == 0 ? cols : (axis == 1 ? rows : 1);
+    if (nout) B200_CUDA(cudaMemsetAsync(out, 0, nout * sizeof(float), s.stream));
+    return B200_OK;
+  }
+  B200_REQUIRE(a != nullptr && ld >= cols, "bad operand");
+  const int64_t need = b200_sum_t_scratch_floats(rows, cols, ld, axis);
+  B200_REQUIRE(need == 0 || (scratch != nullptr && scratch_floats >= need),
+               "sum_t needs %lld floats of scratch, got %lld", (long long)need,
+               (long long)scratch_floats);
+  if (axis == 0) {
+    const bool vec = (cols % 4 == 0) && (ld % 4 == 0) && aligned16(a);
+    // the plan must not depend on the pointer: recompute with the layout-only rule
+    const bool vec_layout = (cols % 4 == 0) && (ld % 4 == 0);
+    int64_t rpc;
+    const int chunks = axis0_plan(rows, cols, vec_layout, &rpc);
+    float* dst = chunks > 1 ? scratch : out;
+    if (vec) {
+      dim3 grid((unsigned)ceil_div(cols, 128), chunks);
+      sum_axis0_pass1<true><<<grid, dim3(32, 8), 0, s.stream>>>(a, rows, cols, ld, rpc, dst);
+    } else {
+      dim3 grid((unsigned)ceil_div(cols, 32), chunks);
+      sum_axis0_pass1<false><<<grid, dim3(32, 8), 0, s.stream>>>(a, rows, cols, ld, rpc, dst);
+    }
+    B200_LAUNCH_CHECK();
+    if (chunks > 1) {
+      sum_axis0_pass2<<<(unsigned)ceil_div(cols, 256), 256, 0, s.stream>>>(scratch, chunks, cols, out);
+      B200_LAUNCH_CHECK();
+    }
+    return B200_OK;
+  }
+  if (axis == 1) {
+    const bool vec = (cols % 4 == 0) && (ld % 4 == 0) && aligned16(a);
+    const unsigned grid = (unsigned)ceil_div(rows, 8);
+    if (vec) sum_axis1_kernel<true><<<grid, 256, 0, s.stream>>>(a, rows, cols, ld, out);
+    else sum_axis1_kernel<false><<<grid, 256, 0, s.stream>>>(a, rows, cols, ld, out);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+  }
+  if (rows == 1 || ld == cols) return sum_all_contiguous(a, rows * cols, out, scratch);
+  // pitched: row sums into scratch[0..rows), then the flat sum of those
+  float* rowsum = scratch + RED_MAX_PARTIALS;
+  sum_axis1_kernel<false><<<(unsigned)ceil_div(rows, 8), 256, 0, s.stream>>>(a, rows, cols, ld, rowsum);
+  B200_LAUNCH_CHECK();
+  return sum_all_contiguous(rowsum, rows, out, scratch);
+}
+
+B200_API int b200_softmax_m(const float* m, float* out, int64_t rows, int64_t cols, int64_t ldm,
+                            int64_t ldo) {
+  if (int rc = require_ready()) return rc;
+  B200_REQUIRE(rows >= 0 && cols >= 0, "negative extent");
+  if (rows * cols == 0) return B200_OK;
+  B200_REQUIRE(m && out && ldm >= cols && ldo >= cols, "bad operand");
+  const State& s = state();
+  const bool vec = (cols % 4 == 0) && (ldm % 4 == 0) && (ldo % 4 == 0) && aligned16(m) && aligned16(out);
+  const int c = (int)cols;
+#define SOFTMAX_CASE(G, VPT)                                                                   \
+  do {                                                                                         \
+    const unsigned grid = (unsigned)ceil_div(rows, 256 / G);                                   \
+    if (vec && VPT >= 4)                                                                       \
+      softmax_rows_kernel<G, (VPT >= 4 ? VPT : 4), true><<<grid, 256, 0, s.stream>>>(m, out, rows, c, ldm, ldo); \
+    else                                                                                       \
+      softmax_rows_kernel<G, VPT, false><<<grid, 256, 0, s.stream>>>(m, out, rows, c, ldm, ldo); \
+  } while (0)
+  if (cols <= 32) SOFTMAX_CASE(32, 1);
+  else if (cols <= 128) SOFTMAX_CASE(32, 4);
+  else if (cols <= 256) SOFTMAX_CASE(32, 8);
+  else if (cols <= 512) SOFTMAX_CASE(32, 16);
+  else if (cols <= 1024) SOFTMAX_CASE(32, 32);
+  else if (cols <= 2048) SOFTMAX_CASE(256, 8);
+  else if (cols <= 4096) SOFTMAX_CASE(256, 16);
+  else if (cols <= 8192) SOFTMAX_CASE(256, 32);
+  else {
+    B200_REQUIRE(rows < ((int64_t)1 << 31), "too many rows");
+    softmax_long_rows_kernel<<<(unsigned)rows, 256, 0, s.stream>>>(m, out, cols, ldm, ldo);
+  }
+#undef SOFTMAX_CASE
+  B200_LAUNCH_CHECK();
+  return B200_OK;
+}
+
+// *flag (device int, caller-zeroed) is set to 1 if any element is Inf or NaN.
+B200_API int b200_nonfinite_flag(const float* a, int64_t rows, int64_t cols, int64_t ld, int* flag) {
+  if (int rc = require_ready()) return rc;
+  B200_REQUIRE(flag != nullptr, "flag is NULL");
+  if (rows * cols <= 0) return B200_OK;
+  const State& s = state();
+  int64_t blocks = ceil_div(rows * cols, 256 * 8);
+  if (blocks > (int64_t)s.sm_count * 8) blocks = (int64_t)s.sm_count * 8;
+  nonfinite_kernel<<<(unsigned)blocks, 256, 0, s.stream>>>(a, rows, cols, ld, flag);
+  B200_LAUNCH_CHECK();
+  return B200_OK;
+}

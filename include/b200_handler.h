@@ -1,0 +1,170 @@
+/* C-ABI of libb200handler.so: the B200 (sm_100a) backend of the brainstorm
+ * Handler API.
+ *
+ * The reference has no FFI on this path: its backends are Python classes that
+ * implement `Handler` (brainstorm/handlers/base_handler.py:13).  Each entry point
+ * below is what a binding of one Handler method binds; the comment names the
+ * abstract method it serves (base_handler.py:LINE) and the CPU implementation it
+ * must agree with (numpy_handler.py:LINE).
+ *
+ * Conventions
+ *  - Every function returns 0 on success, non-zero otherwise; b200_last_error()
+ *    then describes the failure.  Nothing traps on the device.
+ *  - Pointers are device addresses of fp32 data unless stated otherwise.  Work is
+ *    queued on the library's stream in program order; only the functions marked
+ *    "synchronises" wait for it.
+ *  - Elementwise operands are row-pitched 2-D views: `rows` rows of `cols`
+ *    contiguous elements, row r of operand x starting at x + r*ldx.  A contiguous
+ *    array of n elements is passed as rows=1, cols=n.  An output may be the same
+ *    array as an input (in-place forms).  Zero-size extents are valid no-ops.
+ */
+#ifndef B200_HANDLER_H
+#define B200_HANDLER_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- lifecycle / errors ------------------------------------------------- */
+const char* b200_last_error(void);
+int b200_device_count(int* count);
+/* Binds the process to one GPU (one process per GPU), creates the stream and
+ * configures the stream-ordered memory pool.  Fails on anything but sm_100. */
+int b200_init(int device);
+int b200_device_info(int* device, int* sm_count, uint64_t* free_bytes, uint64_t* total_bytes);
+/* key 0: elementwise blocks per SM; 1: elementwise threads per block;
+ * 2: GEMM path (0 auto, 1 CUDA cores, 2 tensor cores only). */
+int b200_set_tuning(int key, int value);
+uint64_t b200_stream(void);
+int b200_sync(void);                                   /* synchronises */
+
+/* ---- memory: Handler.allocate/zeros/ones (base_handler.py:80,102,91;
+ *      numpy_handler.py:36-43: allocate is zero-filled) --------------------- */
+int b200_malloc(uint64_t* ptr, uint64_t bytes, int zero);
+int b200_free(uint64_t ptr);
+int b200_host_alloc(void** ptr, uint64_t bytes);       /* pinned staging memory */
+int b200_host_free(void* ptr);
+
+/* ---- transfers: set_from_numpy / create_from_numpy (base_handler.py:197,145;
+ *      numpy_handler.py:64,54) and get_numpy_copy (base_handler.py:186;
+ *      numpy_handler.py:60) ------------------------------------------------- */
+int b200_memcpy_h2d(uint64_t dst, const void* src, uint64_t bytes);
+int b200_memcpy_d2h(void* dst, uint64_t src, uint64_t bytes);             /* synchronises */
+int b200_memcpy2d_h2d(uint64_t dst, uint64_t dst_pitch, const void* src, uint64_t src_pitch,
+                      uint64_t row_bytes, uint64_t rows);
+int b200_memcpy2d_d2h(void* dst, uint64_t dst_pitch, uint64_t src, uint64_t src_pitch,
+                      uint64_t row_bytes, uint64_t rows);                 /* synchronises */
+
+/* ---- CUDA-event timing on the library stream (benchmark support) --------- */
+int b200_event_create(uint64_t* ev);
+int b200_event_record(uint64_t ev);
+int b200_event_elapsed_ms(uint64_t start, uint64_t stop, float* ms);      /* synchronises */
+int b200_event_destroy(uint64_t ev);
+
+/* ---- copy / fill: base_handler.py:115 (copy_to(src, dest)), :157 (fill);
+ *      numpy_handler.py:47,57 ----------------------------------------------- */
+int b200_copy_to(const float* src, float* dest, int64_t rows, int64_t cols, int64_t lds, int64_t ldd);
+int b200_fill(float* mem, float val, int64_t rows, int64_t cols, int64_t ld);
+
+/* ---- tensor (.) tensor: add_tt :284, subtract_tt :752, mult_tt :683,
+ *      divide_tt :480, modulo_tt :606, mult_add_tt :635 (out += a*b, product and
+ *      sum rounded separately); numpy_handler.py:86,264,245,190,227,233 ------- */
+int b200_add_tt(const float* a, const float* b, float* out, int64_t rows, int64_t cols, int64_t lda, int64_t ldb, int64_t ldo);
+int b200_subtract_tt(const float* a, const float* b, float* out, int64_t rows, int64_t cols, int64_t lda, int64_t ldb, int64_t ldo);
+int b200_mult_tt(const float* a, const float* b, float* out, int64_t rows, int64_t cols, int64_t lda, int64_t ldb, int64_t ldo);
+int b200_divide_tt(const float* a, const float* b, float* out, int64_t rows, int64_t cols, int64_t lda, int64_t ldb, int64_t ldo);
+int b200_modulo_tt(const float* a, const float* b, float* out, int64_t rows, int64_t cols, int64_t lda, int64_t ldb, int64_t ldo);
+int b200_mult_add_tt(const float* a, const float* b, float* out, int64_t rows, int64_t cols, int64_t lda, int64_t ldb, int64_t ldo);
+
+/* ---- scalar (.) tensor: add_st :271, mult_st :670, mult_add_st :622
+ *      (out += s*t); numpy_handler.py:83,242,230 ---------------------------- */
+int b200_add_st(float s, const float* t, float* out, int64_t rows, int64_t cols, int64_t ldt, int64_t ldo);
+int b200_mult_st(float s, const float* t, float* out, int64_t rows, int64_t cols, int64_t ldt, int64_t ldo);
+int b200_mult_add_st(float s, const float* t, float* out, int64_t rows, int64_t cols, int64_t ldt, int64_t ldo);
+
+/* ---- matrix (.) broadcast vector: add_mv :252, subtract_mv :736, mult_mv :649,
+ *      divide_mv :461; mult_add_mv is defined by the backends only
+ *      (numpy_handler.py:239, out += m*v); numpy_handler.py:80,261,236,187.
+ *      v_is_col == 0: v holds `cols` values (a (1, cols) row vector);
+ *      v_is_col == 1: v holds `rows` values (a (rows, 1) column vector).
+ *      broadcast_t :351 / numpy_handler.py:103 copies v along the other axis. */
+int b200_add_mv(const float* m, const float* v, float* out, int64_t rows, int64_t cols, int64_t ldm, int64_t ldo, int v_is_col);
+int b200_subtract_mv(const float* m, const float* v, float* out, int64_t rows, int64_t cols, int64_t ldm, int64_t ldo, int v_is_col);
+int b200_mult_mv(const float* m, const float* v, float* out, int64_t rows, int64_t cols, int64_t ldm, int64_t ldo, int v_is_col);
+int b200_divide_mv(const float* m, const float* v, float* out, int64_t rows, int64_t cols, int64_t ldm, int64_t ldo, int v_is_col);
+int b200_mult_add_mv(const float* m, const float* v, float* out, int64_t rows, int64_t cols, int64_t ldm, int64_t ldo, int v_is_col);
+int b200_broadcast_t(const float* v, float* out, int64_t rows, int64_t cols, int64_t ldo, int v_is_col);
+
+/* ---- unary: abs_t :222, sign_t :697, sqrt_t :724, log_t :545, clip_t :374;
+ *      numpy_handler.py:74,248,258,207,107 ---------------------------------- */
+int b200_abs_t(const float* a, float* out, int64_t rows, int64_t cols, int64_t lda, int64_t ldo);
+int b200_sign_t(const float* a, float* out, int64_t rows, int64_t cols, int64_t lda, int64_t ldo);
+int b200_sqrt_t(const float* a, float* out, int64_t rows, int64_t cols, int64_t lda, int64_t ldo);
+int b200_log_t(const float* a, float* out, int64_t rows, int64_t cols, int64_t lda, int64_t ldo);
+int b200_clip_t(const float* a, float a_min, float a_max, float* out, int64_t rows, int64_t cols, int64_t lda, int64_t ldo);
+
+/* ---- activations: sigmoid :815, tanh :854, rel :786, el :882 and their
+ *      derivatives :827,:867,:799,:903 (dx = dy * f'(y); the x argument of the
+ *      Handler methods is unused by every backend and is not passed);
+ *      numpy_handler.py:277-309 --------------------------------------------- */
+int b200_sigmoid(const float* x, float* y, int64_t rows, int64_t cols, int64_t ldx, int64_t ldy);
+int b200_tanh(const float* x, float* y, int64_t rows, int64_t cols, int64_t ldx, int64_t ldy);
+int b200_rel(const float* x, float* y, int64_t rows, int64_t cols, int64_t ldx, int64_t ldy);
+int b200_el(const float* x, float* y, int64_t rows, int64_t cols, int64_t ldx, int64_t ldy);
+int b200_sigmoid_deriv(const float* y, const float* dy, float* dx, int64_t rows, int64_t cols, int64_t ldy, int64_t lddy, int64_t lddx);
+int b200_tanh_deriv(const float* y, const float* dy, float* dx, int64_t rows, int64_t cols, int64_t ldy, int64_t lddy, int64_t lddx);
+int b200_rel_deriv(const float* y, const float* dy, float* dx, int64_t rows, int64_t cols, int64_t ldy, int64_t lddy, int64_t lddx);
+int b200_el_deriv(const float* y, const float* dy, float* dx, int64_t rows, int64_t cols, int64_t ldy, int64_t lddy, int64_t lddx);
+
+/* ---- predicated: copy_to_if :129, fill_if :168, add_into_if :234;
+ *      numpy_handler.py:173,196,77 (cond != 0 selects) ---------------------- */
+int b200_copy_to_if(const float* src, float* dest, const float* cond, int64_t rows, int64_t cols, int64_t lds, int64_t ldd, int64_t ldc);
+int b200_fill_if(float* mem, float val, const float* cond, int64_t rows, int64_t cols, int64_t ldm, int64_t ldc);
+int b200_add_into_if(const float* a, float* out, const float* cond, int64_t rows, int64_t cols, int64_t lda, int64_t ldo, int64_t ldc);
+
+/* ---- last-axis concat / split-accumulate: merge_tt :560, split_add_tt :712;
+ *      numpy_handler.py:221,251 (contiguous operands) ------------------------ */
+int b200_merge_tt(const float* a, const float* b, float* out, int64_t rows, int64_t na, int64_t nb);
+int b200_split_add_tt(const float* x, float* out_a, float* out_b, int64_t rows, int64_t na, int64_t nb);
+
+/* ---- labels (bit-exact): binarize_v :330, index_m_by_v :522;
+ *      numpy_handler.py:99,202.  Labels are fp32 values holding integers and are
+ *      truncated like astype(int32).  v has one label per row at v + r*ldv.
+ *      index_m_by_v skips rows whose label is outside [0, cols) and sets
+ *      *bad_label_flag (device int, may be NULL) instead of reading out of
+ *      bounds. -------------------------------------------------------------- */
+int b200_binarize_v(const float* v, int64_t ldv, float* out, int64_t rows, int64_t cols, int64_t ldo);
+int b200_index_m_by_v(const float* m, int64_t ldm, const float* v, int64_t ldv, float* out, int64_t ldo, int64_t rows, int64_t cols, int* bad_label_flag);
+
+/* ---- reductions: sum_t :767 / numpy_handler.py:268; softmax_m :843 /
+ *      numpy_handler.py:292; is_fully_finite :210 / numpy_handler.py:69.
+ *      axis 0: out[c] = sum_r a[r,c]; axis 1: out[r] = sum_c a[r,c]; axis -1:
+ *      out[0] = sum of everything.  Sums are deterministic two-pass trees; the
+ *      caller provides the scratch for the partials (size from
+ *      b200_sum_t_scratch_floats, which depends on the extents only). -------- */
+int64_t b200_sum_t_scratch_floats(int64_t rows, int64_t cols, int64_t ld, int axis);
+int b200_sum_t(const float* a, int64_t rows, int64_t cols, int64_t ld, int axis, float* out, float* scratch, int64_t scratch_floats);
+int b200_softmax_m(const float* m, float* out, int64_t rows, int64_t cols, int64_t ldm, int64_t ldo);
+/* ORs 1 into *flag (device int, zeroed by the caller) if any element is Inf/NaN. */
+int b200_nonfinite_flag(const float* a, int64_t rows, int64_t cols, int64_t ld, int* flag);
+
+/* ---- GEMM: dot_mm :444, dot_add_mm :427; numpy_handler.py:181,176.
+ *      out (M x N, row pitch ldo) = or += op(a) . op(b), op(a) is M x K and
+ *      op(b) is K x N; with transa the array a is K x M (pitch lda), with transb
+ *      the array b is N x K (pitch ldb).  out must not overlap a or b. -------- */
+int b200_dot_mm(const float* a, const float* b, float* out, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldo, int transa, int transb);
+int b200_dot_add_mm(const float* a, const float* b, float* out, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldo, int transa, int transb);
+
+/* ---- random: generate_probability_mask :507, fill_gaussian :494;
+ *      numpy_handler.py:199,193.  Device-side Philox4x32-10 streams addressed by
+ *      (seed, offset); the host-RNG parity mode of the Python handler does not
+ *      use these. ----------------------------------------------------------- */
+int b200_generate_probability_mask(float* mask, int64_t n, float probability, uint64_t seed, uint64_t offset);
+int b200_fill_gaussian(float mean, float std, float* out, int64_t n, uint64_t seed, uint64_t offset);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_HANDLER_H */

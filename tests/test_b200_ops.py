@@ -1,0 +1,179 @@
+"""GPU parity of every handler op, through the C-ABI, against (1) the stored
+outputs of the reference's NumpyHandler and (2) the oracle on larger seeded
+inputs.  Mirrors brainstorm/tests/test_handlers_against_reference.py:30-66: all
+array arguments are compared after the call, not only `out`."""
+import os
+
+import numpy as np
+import pytest
+
+import cases as golden_cases
+import parity
+from oracle.numpy_oracle import OracleHandler, op_suite_inputs
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = np.load(os.path.join(os.path.dirname(__file__), 'golden', 'handler_ops.npz'))
+CASES = golden_cases.build_cases()
+
+
+@pytest.fixture(scope='module')
+def H():
+    from brainstorm_b200 import B200Handler
+    return B200Handler(seed=4711, rng_mode='host')
+
+
+def _compare(op, name, got, want, scale=None):
+    if op in parity.BIT_EXACT_OPS:
+        parity.assert_bits_equal(got, want, '%s.%s' % (op, name))
+    elif op in parity.REDUCTION_OPS:
+        parity.assert_reduction_close(got, want, scale, op, name)
+    else:
+        parity.assert_elementwise_close(got, want, op, name)
+
+
+@pytest.mark.parametrize('idx', range(len(CASES)), ids=[c.id for c in CASES])
+def test_op_against_reference_golden(H, idx):
+    c = CASES[idx]
+    if c.op.endswith('_deriv'):
+        c.arrays['y'] = GOLDEN['%d/y' % idx]
+    dev = {k: H.create_from_numpy(v) for k, v in c.arrays.items()}
+    getattr(H, c.op)(*c.bind(dev), **c.kwargs)
+    scale = parity.reduction_scale(c.op, c.arrays, c.kwargs, c.call) \
+        if c.op in parity.REDUCTION_OPS else None
+    for name, d in dev.items():
+        key = '%d/%s' % (idx, name)
+        changed = key in GOLDEN.files and not (name == 'y' and c.op.endswith('_deriv'))
+        want = GOLDEN[key] if key in GOLDEN.files else c.arrays[name]
+        got = H.get_numpy_copy(d)
+        if changed:
+            _compare(c.op, name, got, want, scale)
+        else:  # inputs must come back untouched
+            parity.assert_bits_equal(got, want, '%s.%s (input)' % (c.op, name))
+
+
+def test_host_rng_mode_matches_reference(H):
+    from brainstorm_b200 import B200Handler
+    h = B200Handler(seed=4711, rng_mode='host')
+    mask = h.allocate((6, 50))
+    h.generate_probability_mask(mask, 0.3)
+    gauss = h.allocate((5, 40))
+    h.fill_gaussian(0.5, 2.0, gauss)
+    parity.assert_bits_equal(h.get_numpy_copy(mask), GOLDEN['rng/mask'])
+    parity.assert_bits_equal(h.get_numpy_copy(gauss), GOLDEN['rng/gauss'])
+
+
+def test_device_rng_statistics(H):
+    from brainstorm_b200 import B200Handler
+    h = B200Handler(seed=99, rng_mode='device')
+    mask = h.allocate((1000, 1003))
+    h.generate_probability_mask(mask, 0.3)
+    m = h.get_numpy_copy(mask)
+    assert set(np.unique(m)) <= {0.0, 1.0}
+    assert abs(m.mean() - 0.3) < 3e-3
+    mask2 = h.allocate((1000, 1003))
+    h.generate_probability_mask(mask2, 0.3)
+    assert (h.get_numpy_copy(mask2) != m).mean() > 0.3   # a fresh stream per call
+    g = h.allocate((777, 1001))
+    h.fill_gaussian(1.5, 2.0, g)
+    gg = h.get_numpy_copy(g)
+    assert abs(gg.mean() - 1.5) < 2e-2 and abs(gg.std() - 2.0) < 2e-2
+    assert np.isfinite(gg).all()
+
+
+# ---- the op suite of the benchmark at its CPU-runnable size ----------------------
+def _suite(H, O, rows, cols, seed):
+    d = op_suite_inputs(rows, cols, seed)
+    a, b, dy, row, col, div = d['a'], d['b'], d['dy'], d['row'], d['col'], d['div']
+    labels = d['labels'].astype(np.float32)
+    z = np.zeros_like(a)
+    yield 'add_tt', (a, b, z), {}
+    yield 'subtract_tt', (a, b, z), {}
+    yield 'mult_tt', (a, b, z), {}
+    yield 'divide_tt', (a, div, z), {}
+    yield 'add_mv', (a, row, z), {}
+    yield 'add_mv', (a, col, z), {}
+    yield 'mult_mv', (a, row, z), {}
+    yield 'mult_mv', (a, col, z), {}
+    yield 'mult_st', (0.37, a, z), {}
+    for act in ('sigmoid', 'tanh', 'rel', 'el'):
+        yield act, (a, z), {}
+        y = np.zeros_like(a)
+        getattr(O, act)(a, y)
+        yield act + '_deriv', (a, y, dy, z), {}
+    yield 'sum_t', (a, 0, np.zeros((1, cols), np.float32)), {}
+    yield 'sum_t', (a, 1, np.zeros((rows, 1), np.float32)), {}
+    yield 'sum_t', (a, None, np.zeros((), np.float32)), {}
+    yield 'softmax_m', (a, z), {}
+    yield 'clip_t', (a, -1.0, 1.0, z), {}
+    yield 'abs_t', (a, z), {}
+    yield 'sign_t', (a, z), {}
+    yield 'sqrt_t', (np.abs(a), z), {}
+    yield 'binarize_v', (labels, z), {}
+    yield 'index_m_by_v', (a, labels, np.zeros((rows, 1), np.float32)), {}
+
+
+@pytest.mark.parametrize('rows,cols,seed', [(1024, 1024, 0), (515, 1030, 3), (2048, 205, 5)])
+def test_op_suite_against_oracle(H, rows, cols, seed):
+    O = OracleHandler(np.float32)
+    for op, args, kwargs in _suite(H, O, rows, cols, seed):
+        host = [x.copy() if isinstance(x, np.ndarray) else x for x in args]
+        dev = [H.create_from_numpy(x) if isinstance(x, np.ndarray) else x for x in args]
+        getattr(O, op)(*host, **kwargs)
+        getattr(H, op)(*dev, **kwargs)
+        got = H.get_numpy_copy(dev[-1])
+        want = host[-1]
+        if op == 'sum_t':
+            axis = args[1]
+            absa = np.abs(args[0].astype(np.float64))
+            scale = absa.sum() if axis is None else absa.sum(axis=axis).reshape(want.shape)
+            parity.assert_reduction_close(got, want, scale, op, str(axis))
+            # and at least as close to the exact sum as the float32 CPU result is
+            exact = args[0].astype(np.float64).sum(axis=axis).reshape(want.shape)
+            assert (np.abs(got - exact) <= 1e-5 * scale + 1e-37).all()
+        elif op == 'softmax_m':
+            parity.assert_reduction_close(got, want, 0.0, op)
+        else:
+            _compare(op, 'out', got, want)
+
+
+def test_bad_label_is_reported_not_read(H):
+    m = H.create_from_numpy(np.arange(12, dtype=np.float32).reshape(3, 4))
+    v = H.create_from_numpy(np.array([[1], [7], [2]], np.float32))
+    out = H.zeros((3, 1))
+    H.index_m_by_v(m, v, out)
+    with pytest.raises(IndexError):
+        H.get_numpy_copy(out)
+    # the flag is cleared; the valid rows were still gathered
+    assert H.get_numpy_copy(out).ravel().tolist() == [1.0, 0.0, 10.0]
+
+
+def test_is_fully_finite(H):
+    a = np.random.RandomState(0).randn(300, 70).astype(np.float32)
+    assert H.is_fully_finite(H.create_from_numpy(a))
+    a[299, 69] = np.inf
+    assert not H.is_fully_finite(H.create_from_numpy(a))
+    a[299, 69] = 0
+    a[0, 0] = np.nan
+    assert not H.is_fully_finite(H.create_from_numpy(a))
+    assert H.is_fully_finite(H.allocate((0,)))
+
+
+def test_allocate_is_zero_filled_and_ones(H):
+    assert not H.get_numpy_copy(H.allocate((37, 5))).any()
+    assert (H.get_numpy_copy(H.ones((3, 2, 5))) == 1).all()
+    assert H.get_numpy_copy(H.zeros(())).shape == ()
+
+
+def test_errors_are_exceptions(H):
+    from brainstorm_b200 import B200Error
+    a = H.zeros((4, 4))
+    with pytest.raises(ValueError):
+        H.add_tt(a, H.zeros((4, 5)), a)
+    with pytest.raises(ValueError):
+        H.dot_mm(a, H.zeros((5, 4)), a)
+    with pytest.raises(AssertionError):
+        H.set_from_numpy(a, np.zeros((3, 3)))
+    from brainstorm_b200._lib import lib, check
+    with pytest.raises(B200Error):
+        check(lib.b200_sum_t(a.ptr, 4, 4, 4, 7, a.ptr, 0, 0))
