@@ -48,6 +48,7 @@ struct State {
   int ew_blocks_per_sm = 32;
   int ew_threads = 1024;
   int gemm_path = 0;  // 0 = auto, 1 = force SIMT, 2 = force tensor-core
+  int gemm_bn = 0;    // 0 = auto, else forced tile width (32/64/128)
 };
 State& state();
 int require_ready();

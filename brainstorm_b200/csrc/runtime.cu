@@ -9,6 +9,8 @@
 
 namespace b200 {
 
+int gemm_tc_check_flag();  // gemm_tc.cu: reports a barrier timeout of a tensor-core kernel
+
 static thread_local char g_err[512] = "";
 
 int set_error(int code, const char* fmt, ...) {
@@ -91,6 +93,7 @@ B200_API int b200_set_tuning(int key, int value) {
     case 0: B200_REQUIRE(value >= 1 && value <= 64, "blocks per SM out of range"); s.ew_blocks_per_sm = value; break;
     case 1: B200_REQUIRE(value >= 64 && value <= 1024 && value % 32 == 0, "threads per block out of range"); s.ew_threads = value; break;
     case 2: B200_REQUIRE(value >= 0 && value <= 2, "gemm path must be 0, 1 or 2"); s.gemm_path = value; break;
+    case 3: s.gemm_bn = value; break;
     default: return set_error(B200_ERR_ARG, "unknown tuning key %d", key);
   }
   return B200_OK;
@@ -148,7 +151,7 @@ B200_API int b200_memcpy_d2h(void* dst, uint64_t src, uint64_t bytes) {
                               cudaMemcpyDeviceToHost, state().stream));
   }
   B200_CUDA(cudaStreamSynchronize(state().stream));
-  return B200_OK;
+  return gemm_tc_check_flag();
 }
 
 // Row-pitched transfers for strided views: `rows` rows of `row_bytes` bytes.
@@ -169,13 +172,13 @@ B200_API int b200_memcpy2d_d2h(void* dst, uint64_t dst_pitch, uint64_t src, uint
                                 rows, cudaMemcpyDeviceToHost, state().stream));
   }
   B200_CUDA(cudaStreamSynchronize(state().stream));
-  return B200_OK;
+  return gemm_tc_check_flag();
 }
 
 B200_API int b200_sync(void) {
   if (int rc = require_ready()) return rc;
   B200_CUDA(cudaStreamSynchronize(state().stream));
-  return B200_OK;
+  return gemm_tc_check_flag();
 }
 
 // ---- timing helpers for the benchmark (events on the library stream) --------

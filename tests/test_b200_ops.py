@@ -177,3 +177,67 @@ def test_errors_are_exceptions(H):
     from brainstorm_b200._lib import lib, check
     with pytest.raises(B200Error):
         check(lib.b200_sum_t(a.ptr, 4, 4, 4, 7, a.ptr, 0, 0))
+
+
+# ---- GEMM: tensor-core path (tcgen05 + TMA, 3xTF32) and CUDA-core path ----------------
+GEMM_SHAPES = [(128, 128, 64), (256, 512, 96), (300, 1000, 1000), (128, 4000, 1000),
+               (100, 1200, 784), (1000, 205, 1000), (12, 1000, 12672), (1000, 1000, 2500)]
+
+
+@pytest.mark.parametrize('M,N,K', GEMM_SHAPES, ids=['%dx%dx%d' % s for s in GEMM_SHAPES])
+@pytest.mark.parametrize('path', [0, 1], ids=['auto', 'cuda-core'])
+def test_gemm_all_transposes_against_oracle(H, M, N, K, path):
+    from brainstorm_b200._lib import lib, check
+    O = OracleHandler(np.float32)
+    rs = np.random.RandomState(M + N + K)
+    check(lib.b200_set_tuning(2, path))
+    try:
+        for ta in (False, True):
+            for tb in (False, True):
+                a = rs.randn(*((K, M) if ta else (M, K))).astype(np.float32)
+                b = rs.randn(*((N, K) if tb else (K, N))).astype(np.float32)
+                c0 = rs.randn(M, N).astype(np.float32)
+                scale = np.abs(a.T if ta else a).astype(np.float64) @ np.abs(b.T if tb else b)
+                for op in ('dot_mm', 'dot_add_mm'):
+                    want = c0.copy()
+                    getattr(O, op)(a, b, want, transa=ta, transb=tb)
+                    dc = H.create_from_numpy(c0)
+                    getattr(H, op)(H.create_from_numpy(a), H.create_from_numpy(b), dc, transa=ta, transb=tb)
+                    parity.assert_reduction_close(H.get_numpy_copy(dc), want, scale + np.abs(c0), op,
+                                                  '%s%s' % ('T' if ta else 'N', 'T' if tb else 'N'))
+    finally:
+        check(lib.b200_set_tuning(2, 0))
+
+
+@pytest.mark.parametrize('K', [64, 512, 4096, 16384])
+def test_gemm_same_sign_operands_keep_relative_accuracy(H, K):
+    """All products positive: no cancellation hides a biased accumulation.  The
+    tensor core truncates when it adds into its accumulator; the kernel's chunked
+    drain must keep the bias below the 1e-5 bar for any K."""
+    rs = np.random.RandomState(K)
+    a = rs.uniform(0, 1, (256, K)).astype(np.float32)
+    b = rs.uniform(0, 1, (192, K)).astype(np.float32)
+    out = H.zeros((256, 192))
+    H.dot_mm(H.create_from_numpy(a), H.create_from_numpy(b), out, transb=True)
+    ref = a.astype(np.float64) @ b.astype(np.float64).T
+    rel = np.abs(H.get_numpy_copy(out) - ref) / ref
+    assert rel.max() < 1e-5, rel.max()
+
+
+def test_gemm_views_of_one_flat_buffer(H):
+    """Operands as the memory layer hands them out: slices of one flat allocation
+    at arbitrary element offsets (misaligned ones take the CUDA-core kernel)."""
+    O = OracleHandler(np.float32)
+    rs = np.random.RandomState(11)
+    flat = rs.randn(400000).astype(np.float32)
+    dflat = H.create_from_numpy(flat)
+    for off in (0, 4, 3):
+        a = flat[off:off + 256 * 300].reshape(256, 300)
+        w = flat[100000 + off:100000 + off + 200 * 300].reshape(200, 300)
+        da = dflat[off:off + 256 * 300].reshape((256, 300))
+        dw = dflat[100000 + off:100000 + off + 200 * 300].reshape((200, 300))
+        out = H.zeros((256, 200))
+        want = np.zeros((256, 200), np.float32)
+        H.dot_mm(da, dw, out, transb=True)
+        O.dot_mm(a, w, want, transb=True)
+        parity.assert_reduction_close(H.get_numpy_copy(out), want, np.abs(a) @ np.abs(w.T), 'dot_mm', 'offset %d' % off)
