@@ -1,0 +1,434 @@
+#!/usr/bin/env python
+"""Benchmark of the B200 handler hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (N = 1): the handler op suite on fp32 (65536, 4096) operands (1 GiB each),
+(1, 4096) / (65536, 1) broadcast vectors and 65536 labels in [0, 4096).  One
+"step" runs every op of the suite once.  The metric is the suite's algorithmic
+HBM bytes per second.  With N > 1 ranks (one process per GPU, launched with
+torch.distributed.run) every rank runs the suite on its own (65536, 4096) row
+shard (weak scaling: the global batch is 65536*N rows) and the axis-0 sum is
+completed across shards by an NCCL all-reduce of the (1, 4096) partial sums.
+
+`value` is measured with the operands resident in HBM; `e2e` runs the same suite
+through the public handler API from page-locked HOST buffers, with the
+host->device copies of the operands and the device->host read of the reduction
+results inside the timed region.
+
+`--impl reference` times the CPU restatement of the reference's NumpyHandler
+(oracle/numpy_oracle.py) on a bounded row sample of the same workload, spread
+over all host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+ROWS, COLS = 65536, 4096
+SEED = 1
+CPU_SAMPLE_ROWS = 16384          # bounded sample for the CPU legs (same columns)
+METRIC = 'handler_op_suite_throughput'
+UNIT = 'GB/s'
+
+
+# ------------------------------------------------------------------ op suite
+def suite_bytes(rows, cols):
+    """Algorithmic HBM bytes of each op (4-byte elements): every operand that
+    must be read once plus every result that must be written once."""
+    n = rows * cols
+    e = 4
+    table = [
+        ('add_tt', 3 * n), ('subtract_tt', 3 * n), ('mult_tt', 3 * n), ('divide_tt', 3 * n),
+        ('add_mv_row', 2 * n + cols), ('add_mv_col', 2 * n + rows),
+        ('mult_mv_row', 2 * n + cols), ('mult_mv_col', 2 * n + rows),
+        ('mult_st', 2 * n),
+        ('sigmoid', 2 * n), ('sigmoid_deriv', 3 * n), ('tanh', 2 * n), ('tanh_deriv', 3 * n),
+        ('rel', 2 * n), ('rel_deriv', 3 * n), ('el', 2 * n), ('el_deriv', 3 * n),
+        ('sum_t_axis0', n + cols), ('sum_t_axis1', n + rows), ('sum_t_all', n + 1),
+        ('softmax_m', 2 * n), ('clip_t', 2 * n), ('abs_t', 2 * n), ('sign_t', 2 * n),
+        ('sqrt_t', 2 * n), ('binarize_v', n + rows), ('index_m_by_v', 3 * rows),
+    ]
+    return [(name, cnt * e) for name, cnt in table]
+
+
+def make_suite(H, t):
+    """[(name, thunk)] running each op once on the arrays in dict t."""
+    a, b, dy, div, out, y, absa = t['a'], t['b'], t['dy'], t['div'], t['out'], t['y'], t['absa']
+    row, col, labels = t['row'], t['col'], t['labels']
+    s0, s1, sall, picked = t['s0'], t['s1'], t['sall'], t['picked']
+    return [
+        ('add_tt', lambda: H.add_tt(a, b, out)),
+        ('subtract_tt', lambda: H.subtract_tt(a, b, out)),
+        ('mult_tt', lambda: H.mult_tt(a, b, out)),
+        ('divide_tt', lambda: H.divide_tt(a, div, out)),
+        ('add_mv_row', lambda: H.add_mv(a, row, out)),
+        ('add_mv_col', lambda: H.add_mv(a, col, out)),
+        ('mult_mv_row', lambda: H.mult_mv(a, row, out)),
+        ('mult_mv_col', lambda: H.mult_mv(a, col, out)),
+        ('mult_st', lambda: H.mult_st(0.37, a, out)),
+        ('sigmoid', lambda: H.sigmoid(a, out)),
+        ('sigmoid_deriv', lambda: H.sigmoid_deriv(a, y, dy, out)),
+        ('tanh', lambda: H.tanh(a, out)),
+        ('tanh_deriv', lambda: H.tanh_deriv(a, y, dy, out)),
+        ('rel', lambda: H.rel(a, out)),
+        ('rel_deriv', lambda: H.rel_deriv(a, y, dy, out)),
+        ('el', lambda: H.el(a, out)),
+        ('el_deriv', lambda: H.el_deriv(a, y, dy, out)),
+        ('sum_t_axis0', lambda: H.sum_t(a, 0, s0)),
+        ('sum_t_axis1', lambda: H.sum_t(a, 1, s1)),
+        ('sum_t_all', lambda: H.sum_t(a, None, sall)),
+        ('softmax_m', lambda: H.softmax_m(a, out)),
+        ('clip_t', lambda: H.clip_t(a, -1.0, 1.0, out)),
+        ('abs_t', lambda: H.abs_t(a, out)),
+        ('sign_t', lambda: H.sign_t(a, out)),
+        ('sqrt_t', lambda: H.sqrt_t(absa, out)),
+        ('binarize_v', lambda: H.binarize_v(labels, out)),
+        ('index_m_by_v', lambda: H.index_m_by_v(a, labels, picked)),
+    ]
+
+
+def host_inputs(rows, cols, seed, alloc=None):
+    """Seeded synthetic operands.  A (rows/16, cols) block is drawn from the seeded
+    generator and tiled down the rows: the value distribution is the workload's
+    (uniform[-4, 4]; divisors uniform[0.5, 4] with a random sign; labels uniform in
+    [0, cols)) and generating 4 GiB of random numbers does not dominate start-up."""
+    from oracle.numpy_oracle import op_suite_inputs
+    block_rows = max(rows // 16, 1)
+    blk = op_suite_inputs(block_rows, cols, seed)
+    reps = -(-rows // block_rows)
+    alloc = alloc or (lambda shape: np.empty(shape, np.float32))
+    d = {}
+    for k in ('a', 'b', 'dy', 'div'):
+        full = alloc((rows, cols))
+        for r in range(reps):
+            lo = r * block_rows
+            hi = min(rows, lo + block_rows)
+            full[lo:hi] = blk[k][:hi - lo]
+        d[k] = full
+    d['row'] = blk['row']
+    d['col'] = np.tile(blk['col'], (reps, 1))[:rows].copy()
+    d['labels'] = np.tile(blk['labels'], (reps, 1))[:rows].astype(np.float32)
+    return d
+
+
+# ------------------------------------------------------------------ clocks
+class ClockSampler(object):
+    QUERY = ('index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,'
+             'clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,'
+             'clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, gpu_index):
+        self.rows = []
+        self.proc = None
+        self.gpu = gpu_index
+        try:
+            self.proc = subprocess.Popen(
+                ['nvidia-smi', '-i', str(gpu_index), '--query-gpu=' + self.QUERY,
+                 '--format=csv,noheader,nounits', '-lms', '100'],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), line.strip()))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], None, set()
+        names = ['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap']
+        for ts, line in self.rows:
+            if ts < t0 or ts > t1 + 0.2:
+                continue
+            f = [x.strip() for x in line.split(',')]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx = float(f[2])
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith('active'):
+                    reasons.add(name)
+        return {'sm_mhz': float(np.median(sm)) if sm else None, 'sm_max_mhz': mx,
+                'reasons': sorted(reasons), 'samples': len(sm)}
+
+
+# ------------------------------------------------------------------ CPU legs
+def cpu_suite_time(rows, cols, seed, threads, steps, warmup):
+    """Times the oracle (CPU restatement of NumpyHandler) on `rows` rows, split
+    into row chunks over `threads` host threads (numpy releases the GIL)."""
+    from concurrent.futures import ThreadPoolExecutor
+    from oracle.numpy_oracle import OracleHandler, op_suite_inputs
+    O = OracleHandler(np.float32)
+    d = op_suite_inputs(rows, cols, seed)
+    labels = d['labels'].astype(np.float32)
+    y = np.zeros_like(d['a'])
+    O.tanh(d['a'], y)
+    absa = np.abs(d['a'])
+    bounds = np.linspace(0, rows, threads + 1).astype(int)
+    chunks = []
+    for i in range(threads):
+        lo, hi = bounds[i], bounds[i + 1]
+        if hi <= lo:
+            continue
+        t = {k: d[k][lo:hi] for k in ('a', 'b', 'dy', 'div')}
+        t.update(out=np.zeros((hi - lo, cols), np.float32), y=y[lo:hi], absa=absa[lo:hi],
+                 row=d['row'], col=d['col'][lo:hi], labels=labels[lo:hi],
+                 s0=np.zeros((1, cols), np.float32), s1=np.zeros((hi - lo, 1), np.float32),
+                 sall=np.zeros((), np.float32), picked=np.zeros((hi - lo, 1), np.float32))
+        chunks.append(make_suite(O, t))
+
+    def run_chunk(suite):
+        for _, fn in suite:
+            fn()
+
+    def step(pool):
+        list(pool.map(run_chunk, chunks))
+
+    with ThreadPoolExecutor(max_workers=threads) as pool:
+        for _ in range(warmup):
+            step(pool)
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            step(pool)
+        dt = (time.perf_counter() - t0) / steps
+    nbytes = sum(b for _, b in suite_bytes(rows, cols))
+    return nbytes / dt / 1e9, dt
+
+
+def run_reference(args):
+    rank = int(os.environ.get('RANK', '0'))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    steps = max(1, min(args.steps, 5))
+    gbs, dt = cpu_suite_time(CPU_SAMPLE_ROWS, COLS, SEED, threads, steps, min(args.warmup, 1))
+    sample = '%d of %d rows per step (same %d columns, same ops), %d steps' % (
+        CPU_SAMPLE_ROWS, ROWS, COLS, steps)
+    line = {
+        'impl': 'reference', 'metric': METRIC, 'value': round(gbs, 3), 'unit': UNIT,
+        'n_gpus': args.gpus, 'steps': steps, 'warmup': min(args.warmup, 1),
+        'ms_per_step': round(dt * 1e3, 3), 'higher_is_better': True, 'scaling': 'weak',
+        'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic (seeded)',
+        'config': {'workload': 'handler op suite, fp32 (%d, %d) operands' % (ROWS, COLS),
+                   'sample_rows': CPU_SAMPLE_ROWS, 'cols': COLS, 'seed': SEED},
+        'cpu_baseline': {'value': round(gbs, 3), 'unit': UNIT, 'cores': threads, 'kind': 'port',
+                         'sample': sample},
+        'e2e': {'value': round(gbs, 3), 'unit': UNIT, 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+        'gpu_launches': 0,
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------ GPU arm
+def run_b200(args):
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    rank = int(os.environ.get('RANK', '0'))
+    local_rank = int(os.environ.get('LOCAL_RANK', '0'))
+    if world != args.gpus:
+        if args.gpus != 1 or world != 1:
+            raise SystemExit('--gpus %d needs WORLD_SIZE=%d (launch with torch.distributed.run)' % (args.gpus, args.gpus))
+    import torch
+    import torch.distributed as dist
+    from brainstorm_b200 import B200Handler, lib
+    from brainstorm_b200._lib import check
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group('nccl', device_id=torch.device('cuda', local_rank))
+    H = B200Handler(seed=SEED + rank, device=local_rank)
+
+    def barrier():
+        check(lib.b200_sync())
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def new_event():
+        e = ctypes.c_uint64()
+        check(lib.b200_event_create(ctypes.byref(e)))
+        return e.value
+
+    def elapsed(e0, e1):
+        ms = ctypes.c_float()
+        check(lib.b200_event_elapsed_ms(e0, e1, ctypes.byref(ms)))
+        return ms.value
+
+    # ---- operands: page-locked host copies (for e2e) and device-resident arrays
+    host = host_inputs(ROWS, COLS, SEED + rank, alloc=H.pinned_empty)
+    t = {k: H.create_from_numpy(v) for k, v in host.items()}
+    t['out'] = H.zeros((ROWS, COLS))
+    t['y'] = H.zeros((ROWS, COLS))
+    t['absa'] = H.zeros((ROWS, COLS))
+    H.tanh(t['a'], t['y'])
+    H.abs_t(t['a'], t['absa'])
+    t['s0'] = H.zeros((1, COLS))
+    t['s1'] = H.zeros((ROWS, 1))
+    t['sall'] = H.zeros(())
+    t['picked'] = H.zeros((ROWS, 1))
+    suite = make_suite(H, t)
+    nbytes = dict(suite_bytes(ROWS, COLS))
+    step_bytes = sum(nbytes.values())
+
+    if world > 1:
+        s0_torch = torch.as_tensor(t['s0'], device='cuda')
+
+    def finish_axis0():
+        """Cross-shard completion of the axis-0 sum: all-reduce of (1, COLS)."""
+        if world > 1:
+            check(lib.b200_sync())
+            dist.all_reduce(s0_torch)
+            torch.cuda.current_stream().synchronize()
+
+    def step(events=None):
+        for i, (name, fn) in enumerate(suite):
+            if events is not None:
+                check(lib.b200_event_record(events[i][0]))
+            fn()
+            if name == 'sum_t_axis0':
+                finish_axis0()
+            if events is not None:
+                check(lib.b200_event_record(events[i][1]))
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+
+    # ---- device-resident timing: K steps, per-op events inside the timed region
+    per_step_events = [[(new_event(), new_event()) for _ in suite] for _ in range(args.steps)]
+    e_start, e_stop = new_event(), new_event()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    launches0 = lib.b200_launch_count()
+    barrier()
+    t0 = time.time()
+    check(lib.b200_event_record(e_start))
+    for k in range(args.steps):
+        step(per_step_events[k])
+    check(lib.b200_event_record(e_stop))
+    barrier()
+    t1 = time.time()
+    launches = lib.b200_launch_count() - launches0
+    total_ms = elapsed(e_start, e_stop)
+    clocks = sampler.stop(t0, t1) if sampler else None
+    if world > 1:
+        tt = torch.tensor([total_ms], device='cuda')
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        total_ms = float(tt.item())
+    ms_per_step = total_ms / args.steps
+    value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
+
+    op_ms = {}
+    for i, (name, _) in enumerate(suite):
+        op_ms[name] = float(np.mean([elapsed(*per_step_events[k][i]) for k in range(args.steps)]))
+    ops = {name: {'ms': round(ms, 4), 'gbs': round(nbytes[name] / (ms * 1e-3) / 1e9, 1)}
+           for name, ms in op_ms.items()}
+
+    # ---- end to end: host buffers in, results out, every step
+    e2e_steps = max(1, min(args.steps, 3))
+    results = [np.empty((1, COLS), np.float32), np.empty((ROWS, 1), np.float32),
+               np.empty((), np.float32), np.empty((ROWS, 1), np.float32)]
+    h2d = sum(host[k].nbytes for k in ('a', 'b', 'dy', 'div', 'row', 'col', 'labels'))
+    d2h = sum(r.nbytes for r in results)
+
+    def e2e_step():
+        for k in ('a', 'b', 'dy', 'div', 'row', 'col', 'labels'):
+            H.set_from_numpy(t[k], host[k])
+        step()
+        for r, key in zip(results, ('s0', 's1', 'sall', 'picked')):
+            r[...] = H.get_numpy_copy(t[key])
+
+    e2e_step()
+    barrier()
+    w0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    barrier()
+    e2e_s = (time.perf_counter() - w0) / e2e_steps
+    if world > 1:
+        tt = torch.tensor([e2e_s], device='cuda')
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        e2e_s = float(tt.item())
+    e2e_value = world * step_bytes / e2e_s / 1e9
+
+    if rank == 0:
+        peaks, peak_src = None, 'fallback'
+        try:
+            with open(os.path.join(ROOT, 'MEASURED_PEAKS.json')) as f:
+                peaks = json.load(f)
+            peak, peak_src = float(peaks['hbm_gbs']), 'measured'
+        except Exception:
+            peak = 6650.0
+        traffic = None
+        try:
+            with open(os.path.join(ROOT, 'profiles', 'ncu_traffic.json')) as f:
+                traffic = json.load(f).get('ew_flat_vec_add_tt_bytes_per_launch_1gib')
+        except Exception:
+            pass
+        dom = 'add_tt'
+        achieved = nbytes[dom] / (op_ms[dom] * 1e-3) / 1e9
+        cpu = None
+        if world == 1 or True:
+            threads = os.cpu_count() or 1
+            cgbs, cdt = cpu_suite_time(CPU_SAMPLE_ROWS, COLS, SEED, threads, 2, 1)
+            cpu = {'value': round(cgbs, 3), 'unit': UNIT, 'cores': threads, 'kind': 'port',
+                   'sample': '%d of %d rows per step (same %d columns, same ops), 2 steps after 1 warm-up, '
+                             'row chunks over %d threads' % (CPU_SAMPLE_ROWS, ROWS, COLS, threads)}
+        line = {
+            'metric': METRIC, 'value': round(value, 1), 'unit': UNIT, 'n_gpus': world,
+            'steps': args.steps, 'warmup': max(args.warmup, 3), 'ms_per_step': round(ms_per_step, 4),
+            'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32',
+            'data': 'synthetic (seeded block tiled down the rows)',
+            'config': {'workload': 'handler op suite (27 ops), fp32 (%d, %d) operands per GPU, '
+                                   '1 GiB each' % (ROWS, COLS),
+                       'rows_per_gpu': ROWS, 'cols': COLS, 'seed': SEED,
+                       'l2': 'operands (1 GiB) exceed L2 (126 MB); no flush needed',
+                       'sharding': 'rows; axis-0 sum all-reduced over NCCL' if world > 1 else 'single GPU'},
+            'e2e': {'value': round(e2e_value, 1), 'unit': UNIT, 'h2d_bytes_per_step': int(h2d),
+                    'd2h_bytes_per_step': int(d2h), 'steps': e2e_steps},
+            'gpu_launches': int(launches),
+            'clocks': clocks,
+            'roofline': {'bound': 'hbm', 'kernel': 'ew_flat_vec<FAdd> (add_tt)', 'achieved': round(achieved, 1),
+                         'peak': peak, 'peak_source': peak_src, 'unit': 'GB/s',
+                         'frac': round(achieved / peak, 4), 'traffic': traffic},
+            'cpu_baseline': cpu,
+            'ops': ops,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=30)
+    ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
+    args = ap.parse_args()
+    if args.impl == 'reference':
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == '__main__':
+    main()

@@ -3,11 +3,19 @@
     from brainstorm_b200 import B200Handler
     net.set_handler(B200Handler())
 
-Importing the package loads ``libb200handler.so`` (build it with
-``python -m brainstorm_b200.build``); there is no CPU fallback.
+The first use of any name below loads ``libb200handler.so`` (build it with
+``python -m brainstorm_b200.build``); there is no CPU fallback.  The names are
+resolved lazily so that the build module can be run before the library exists.
 """
-from ._lib import B200Error, lib  # noqa: F401
-from .array import B200Array  # noqa: F401
-from .handler import B200Handler  # noqa: F401
+__all__ = ['B200Handler', 'B200Array', 'B200Error', 'lib']
 
-__all__ = ['B200Handler', 'B200Array', 'B200Error']
+_HOME = {'B200Handler': 'handler', 'B200Array': 'array', 'B200Error': '_lib', 'lib': '_lib'}
+
+
+def __getattr__(name):
+    if name in _HOME:
+        import importlib
+        value = getattr(importlib.import_module('.' + _HOME[name], __name__), name)
+        globals()[name] = value
+        return value
+    raise AttributeError('module %r has no attribute %r' % (__name__, name))

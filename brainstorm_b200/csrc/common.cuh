@@ -35,8 +35,12 @@ int cuda_fail(cudaError_t e, const char* what, const char* file, int line);
   } while (0)
 
 // Checks the launch that has just been issued (asynchronous errors surface at
-// the next synchronising call).
-#define B200_LAUNCH_CHECK() B200_CUDA(cudaGetLastError())
+// the next synchronising call) and counts it (b200_launch_count).
+#define B200_LAUNCH_CHECK()            \
+  do {                                 \
+    ++b200::state().launches;          \
+    B200_CUDA(cudaGetLastError());     \
+  } while (0)
 
 // ---- per-process state ----------------------------------------------------
 struct State {
@@ -44,6 +48,7 @@ struct State {
   int device = -1;
   int sm_count = 148;
   cudaStream_t stream = nullptr;
+  uint64_t launches = 0;  // kernels launched by this library so far
   // tuning knobs (b200_set_tuning)
   int ew_blocks_per_sm = 32;
   int ew_threads = 1024;

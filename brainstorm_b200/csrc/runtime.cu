@@ -99,6 +99,8 @@ B200_API int b200_set_tuning(int key, int value) {
   return B200_OK;
 }
 
+B200_API uint64_t b200_launch_count(void) { return state().launches; }
+
 B200_API uint64_t b200_stream(void) { return (uint64_t)(uintptr_t)state().stream; }
 
 B200_API int b200_malloc(uint64_t* ptr, uint64_t bytes, int zero) {

@@ -38,6 +38,8 @@ int b200_device_info(int* device, int* sm_count, uint64_t* free_bytes, uint64_t*
  * 2: GEMM path (0 auto, 1 CUDA cores, 2 tensor cores only). */
 int b200_set_tuning(int key, int value);
 uint64_t b200_stream(void);
+/* Number of kernels this library has launched in this process so far. */
+uint64_t b200_launch_count(void);
 int b200_sync(void);                                   /* synchronises */
 
 /* ---- memory: Handler.allocate/zeros/ones (base_handler.py:80,102,91;
