@@ -426,3 +426,59 @@ B200_API int b200_nonfinite_flag(const float* a, int64_t rows, int64_t cols, int
   B200_LAUNCH_CHECK();
   return B200_OK;
 }
+
+// ---- sum_t without any allocation ------------------------------------------------------
+// Some hosts of this library may not allocate device memory once they are running:
+// a serving process whose own memory pool has already taken the whole GPU, or a
+// control loop that must never enter the CUDA allocator because an allocation can
+// fail or stall the device at an arbitrary moment.  For them the partial sums of
+// the two-pass tree live in a fixed array inside the library image instead of in
+// caller-provided scratch.  Every GPU that loads the library carries the array
+// (1 MiB) until the process exits.
+#define B200_STATIC_SCRATCH_FLOATS (256 * 1024)
+static __device__ __align__(256) float g_static_sum_scratch[B200_STATIC_SCRATCH_FLOATS];
+
+namespace b200 {
+// In host code the symbol above is only a stand-in, not a device address; the real
+// address is asked for once per device (with that device current) and kept here.
+static float* g_static_scratch_ptr[64] = {nullptr};
+
+static int static_scratch(float** out) {
+  int dev = -1;
+  B200_CUDA(cudaGetDevice(&dev));
+  B200_REQUIRE(dev >= 0 && dev < 64, "device ordinal %d out of range", dev);
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    B200_CUDA(cudaGetSymbolAddress((void**)&p, g_static_sum_scratch));
+    B200_REQUIRE(p != nullptr, "cudaGetSymbolAddress returned a NULL address");
+    g_static_scratch_ptr[dev] = p;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return B200_OK;
+}
+}  // namespace b200
+
+B200_API int64_t b200_sum_t_static_max_scratch_floats(void) { return B200_STATIC_SCRATCH_FLOATS; }
+
+// Same result as b200_sum_t (same kernels, same order of additions), but the
+// partial sums go to the library's built-in array: the call allocates nothing.
+// Extents whose partials need more than the array holds are rejected.  The first
+// call on a device looks up the array's device address; make that call before
+// any stream capture begins.  All calls share the one array, which keeps the
+// previous call's partials: nothing in it has to start at zero (pass 1 writes every
+// partial that pass 2 reads), but two such calls that overlap on the GPU (different
+// streams or processes' threads) race on it.
+B200_API int b200_sum_t_static(const float* a, int64_t rows, int64_t cols, int64_t ld, int axis,
+                               float* out) {
+  if (int rc = require_ready()) return rc;
+  B200_REQUIRE(axis == 0 || axis == 1 || axis == -1, "axis must be 0, 1 or -1 (all)");
+  const int64_t need = b200_sum_t_scratch_floats(rows, cols, ld, axis);
+  B200_REQUIRE(need <= B200_STATIC_SCRATCH_FLOATS,
+               "sum_t over (%lld, %lld) axis %d needs %lld floats of scratch; the built-in array "
+               "holds %lld: use b200_sum_t with caller-provided scratch",
+               (long long)rows, (long long)cols, axis, (long long)need,
+               (long long)B200_STATIC_SCRATCH_FLOATS);
+  float* scratch = nullptr;
+  if (int rc = static_scratch(&scratch)) return rc;
+  return b200_sum_t(a, rows, cols, ld, axis, out, scratch, B200_STATIC_SCRATCH_FLOATS);
+}

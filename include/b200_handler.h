@@ -148,6 +148,15 @@ int b200_index_m_by_v(const float* m, int64_t ldm, const float* v, int64_t ldv, 
  *      b200_sum_t_scratch_floats, which depends on the extents only). -------- */
 int64_t b200_sum_t_scratch_floats(int64_t rows, int64_t cols, int64_t ld, int axis);
 int b200_sum_t(const float* a, int64_t rows, int64_t cols, int64_t ld, int axis, float* out, float* scratch, int64_t scratch_floats);
+/* No counterpart in the reference.  sum_t for hosts that may not allocate device
+ * memory while running (their own pool already owns the GPU, or they must never
+ * enter the CUDA allocator): the partial sums go to a 1 MiB array built into the
+ * library instead of caller scratch; the call allocates nothing.  Same result as
+ * b200_sum_t.  Extents that need more than b200_sum_t_static_max_scratch_floats()
+ * are rejected.  The first call on a device resolves the array's address: make it
+ * before any stream capture.  Calls share the array; overlapping calls race. */
+int64_t b200_sum_t_static_max_scratch_floats(void);
+int b200_sum_t_static(const float* a, int64_t rows, int64_t cols, int64_t ld, int axis, float* out);
 int b200_softmax_m(const float* m, float* out, int64_t rows, int64_t cols, int64_t ldm, int64_t ldo);
 /* ORs 1 into *flag (device int, zeroed by the caller) if any element is Inf/NaN. */
 int b200_nonfinite_flag(const float* a, int64_t rows, int64_t cols, int64_t ld, int* flag);
