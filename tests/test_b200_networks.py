@@ -1,0 +1,83 @@
+"""The reference's own layers, Network and steppers, unchanged, on B200Handler
+(installed through Network.set_handler) against the same stack on NumpyHandler."""
+import numpy as np
+import pytest
+
+from conftest import needs_reference
+
+pytestmark = [pytest.mark.gpu, needs_reference]
+
+
+def _pair(builder, **kw):
+    import brainstorm as bs
+    from brainstorm.handlers import NumpyHandler
+    from brainstorm_b200 import B200Handler
+    net_cpu, data, stepper = builder(**kw)
+    net_cpu.set_handler(NumpyHandler(np.float32, seed=77))
+    net_gpu, _, _ = builder(**kw)
+    net_gpu.set_handler(B200Handler(seed=77, rng_mode='host'))
+    p_cpu = net_cpu.get('parameters')
+    p_gpu = net_gpu.get('parameters')
+    assert np.array_equal(p_cpu, p_gpu)
+    return net_cpu, net_gpu, data, stepper
+
+
+def _close(got, want, rtol, what):
+    scale = np.abs(want).max() + 1e-30
+    err = np.abs(got - want).max()
+    assert err <= rtol * scale, '%s: max err %.3g vs scale %.3g' % (what, err, scale)
+
+
+def _check_training(builder, steps, rtol, **kw):
+    from brainstorm_b200.workloads import train_steps
+    net_cpu, net_gpu, data, stepper = _pair(builder, **kw)
+    # one forward/backward: loss, every gradient
+    for net in (net_cpu, net_gpu):
+        net.provide_external_data(data)
+        net.forward_pass(training_pass=True)
+        net.backward_pass()
+    l_cpu = float(net_cpu.get_loss_values()['total_loss'])
+    l_gpu = float(net_gpu.get_loss_values()['total_loss'])
+    assert abs(l_cpu - l_gpu) <= 1e-5 * abs(l_cpu), (l_cpu, l_gpu)
+    _close(net_gpu.get('gradients'), net_cpu.get('gradients'), rtol, 'gradients')
+    # a few optimiser steps: losses and parameters stay together
+    lc = train_steps(net_cpu, data, stepper(), steps)
+    lg = train_steps(net_gpu, data, stepper(), steps)
+    np.testing.assert_allclose(lg, lc, rtol=2e-4)
+    _close(net_gpu.get('parameters'), net_cpu.get('parameters'), 10 * rtol, 'parameters')
+    return net_cpu, net_gpu
+
+
+def test_mlp_dropout_fc_softmax_momentum():
+    from brainstorm_b200 import workloads
+    _check_training(workloads.mlp, steps=3, rtol=1e-4, batch=100)
+
+
+def test_lstm_two_layers_sgd():
+    from brainstorm_b200 import workloads
+    _check_training(workloads.lstm, steps=2, rtol=2e-4, time=7, batch=9, vocab=23, hidden=32)
+
+
+def test_lstm_aligned_sizes_use_tensor_cores():
+    from brainstorm_b200 import workloads
+    _check_training(workloads.lstm, steps=2, rtol=2e-4, time=6, batch=64, vocab=48, hidden=128)
+
+
+def test_highway_batchnorm_stack():
+    from brainstorm_b200 import workloads
+    _check_training(workloads.highway_bn, steps=2, rtol=2e-4, batch=96, width=64, classes=10, blocks=3)
+
+
+def test_handler_is_describable_and_weight_modifier_runs():
+    import brainstorm as bs
+    from brainstorm.describable import get_description, create_from_description
+    from brainstorm_b200 import B200Handler, workloads
+    h = B200Handler(seed=5)
+    d = get_description(h)
+    assert d == {'@type': 'B200Handler'}
+    assert isinstance(create_from_description(d), B200Handler)
+    net_cpu, net_gpu, data, stepper = _pair(workloads.mlp, batch=20, hidden=64)
+    for net in (net_cpu, net_gpu):   # examples/mnist_pi.py:42
+        net.set_weight_modifiers({'FC': {'W': bs.value_modifiers.ConstrainL2Norm(0.5)}})
+        net.apply_weight_modifiers()
+    _close(net_gpu.get('parameters'), net_cpu.get('parameters'), 1e-5, 'constrained parameters')
