@@ -407,6 +407,27 @@ splitk_reduce_kernel(const float* __restrict__ partial, int splits, int64_t spli
   }
 }
 
+// Copy of a row-pitched matrix whose base or pitch TMA cannot address (base not on a
+// 16-byte boundary, pitch not a multiple of 4 floats) into an aligned, padded
+// temporary: dst row pitch ldd is a multiple of 4, the pad columns are zero.
+__global__ void __launch_bounds__(256)
+stage_operand_kernel(const float* __restrict__ src, int64_t rows, int64_t cols, int64_t lds,
+                     float* __restrict__ dst, int64_t ldd) {
+  const int64_t groups_per_row = ldd >> 2;
+  const int64_t total = rows * groups_per_row;
+  for (int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; g < total;
+       g += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = g / groups_per_row, c = (g - r * groups_per_row) << 2;
+    const float* p = src + r * lds + c;
+    float4 v;
+    v.x = (c < cols) ? p[0] : 0.f;
+    v.y = (c + 1 < cols) ? p[1] : 0.f;
+    v.z = (c + 2 < cols) ? p[2] : 0.f;
+    v.w = (c + 3 < cols) ? p[3] : 0.f;
+    *reinterpret_cast<float4*>(dst + r * ldd + c) = v;
+  }
+}
+
 // ---- host side ---------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
@@ -499,21 +520,49 @@ int gemm_tc_check_flag() {
   return B200_OK;
 }
 
-static bool tc_eligible(int transa, int transb, int64_t M, int64_t N, int64_t K, const float* a, int64_t lda,
-                        const float* b, int64_t ldb) {
-  (void)transa; (void)transb;
-  if (!aligned16(a) || !aligned16(b) || (lda % 4) || (ldb % 4)) return false;
-  // tiny problems: the CUDA-core kernel has less fixed cost
-  if (M * N * K < (int64_t)64 * 64 * 64) return false;
-  return true;
+// Views handed out by the reference's memory layer start at arbitrary element
+// offsets of one flat buffer, so most operands are NOT on a 16-byte boundary.  Such
+// an operand (or one whose pitch is not a multiple of 4 floats, e.g. 205 columns) is
+// first copied into an aligned stream-ordered temporary; the copy moves 8 bytes per
+// element against the 2*N (or 2*M) flops per element of the GEMM that follows.
+struct Staged {
+  const float* ptr = nullptr;
+  int64_t ld = 0;
+  float* temp = nullptr;
+};
+static int stage_if_needed(const float* p, int64_t rows, int64_t cols, int64_t ld, Staged* out) {
+  out->ptr = p;
+  out->ld = ld;
+  out->temp = nullptr;
+  if (aligned16(p) && ld % 4 == 0) return B200_OK;
+  const State& s = state();
+  const int64_t ldd = (cols + 3) & ~(int64_t)3;
+  B200_CUDA(cudaMallocAsync((void**)&out->temp, (size_t)rows * ldd * sizeof(float), s.stream));
+  int64_t blocks = ceil_div(rows * (ldd >> 2), 256);
+  if (blocks > (int64_t)s.sm_count * 16) blocks = (int64_t)s.sm_count * 16;
+  stage_operand_kernel<<<(unsigned)blocks, 256, 0, s.stream>>>(p, rows, cols, ld, out->temp, ldd);
+  B200_LAUNCH_CHECK();
+  out->ptr = out->temp;
+  out->ld = ldd;
+  return B200_OK;
+}
+static void release(Staged* st) {
+  if (st->temp) cudaFreeAsync(st->temp, state().stream);
+  st->temp = nullptr;
 }
 
 int gemm_tc(int transa, int transb, int64_t M, int64_t N, int64_t K, const float* a, int64_t lda,
             const float* b, int64_t ldb, float* c, int64_t ldc, int accumulate) {
-  if (!tc_eligible(transa, transb, M, N, K, a, lda, b, ldb)) return B200_ERR_UNSUPPORTED;
+  // tiny problems: the CUDA-core kernel has less fixed cost
+  if (M * N * K < (int64_t)64 * 64 * 64 && state().gemm_path != 2) return B200_ERR_UNSUPPORTED;
   std::lock_guard<std::mutex> lock(tc_host().mu);
   if (int rc = tc_setup()) return rc;
   const State& s = state();
+  Staged sa, sb;
+  if (int rc = stage_if_needed(a, transa ? K : M, transa ? M : K, lda, &sa)) return rc;
+  if (int rc = stage_if_needed(b, transb ? N : K, transb ? K : N, ldb, &sb)) { release(&sa); return rc; }
+  a = sa.ptr; lda = sa.ld;
+  b = sb.ptr; ldb = sb.ld;
   // Tile width.  One tcgen05.mma costs about the same time for any N <= 128 (it is
   // bound by streaming the 128-row A operand), so the tile is as wide as N allows.
   const int64_t tiles_m = ceil_div(M, TC_BM);
@@ -551,9 +600,9 @@ int gemm_tc(int transa, int transb, int64_t M, int64_t N, int64_t K, const float
   }
   CUtensorMap ma, mb;
   // A: K-major when not transposed (array is M x K), MN-major when transposed (K x M)
-  if (int rc = transa ? tc_map(a, M, K, lda, TC_BK, 1, &ma) : tc_map(a, K, M, lda, TC_BM, 0, &ma)) return rc;
+  if (int rc = transa ? tc_map(a, M, K, lda, TC_BK, 1, &ma) : tc_map(a, K, M, lda, TC_BM, 0, &ma)) { release(&sa); release(&sb); return rc; }
   // B: K-major when transposed (array is N x K), MN-major when not (K x N)
-  if (int rc = transb ? tc_map(b, K, N, ldb, bn, 0, &mb) : tc_map(b, N, K, ldb, TC_BK, 1, &mb)) return rc;
+  if (int rc = transb ? tc_map(b, K, N, ldb, bn, 0, &mb) : tc_map(b, N, K, ldb, TC_BK, 1, &mb)) { release(&sa); release(&sb); return rc; }
   dim3 grid((unsigned)ceil_div(N, bn), (unsigned)tiles_m, (unsigned)splits);
   int* flag = tc_host().error_flag_dev;
   const int m = (int)M, n = (int)N, k = (int)K;
@@ -570,6 +619,8 @@ int gemm_tc(int transa, int transb, int64_t M, int64_t N, int64_t K, const float
     if (blocks > (int64_t)s.sm_count * 8) blocks = (int64_t)s.sm_count * 8;
     splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, s.stream>>>(dst, splits, split_stride, c, M, N, dst_ld, ldc, accumulate);
   }
+  release(&sa);
+  release(&sb);
   B200_LAUNCH_CHECK();
   return B200_OK;
 }
