@@ -551,10 +551,20 @@ static void release(Staged* st) {
   st->temp = nullptr;
 }
 
-int gemm_tc(int transa, int transb, int64_t M, int64_t N, int64_t K, const float* a, int64_t lda,
-            const float* b, int64_t ldb, float* c, int64_t ldc, int accumulate) {
-  // tiny problems: the CUDA-core kernel has less fixed cost
-  if (M * N * K < (int64_t)64 * 64 * 64 && state().gemm_path != 2) return B200_ERR_UNSUPPORTED;
+// Where a GEMM left its result when the caller asked to finish split-K itself:
+// `splits` partial matrices of pitch ld, split_stride floats apart, to be added in
+// index order.  The buffer belongs to the library and is valid until the next GEMM
+// on the stream.
+struct GemmPartials {
+  const float* ptr;
+  int splits;
+  int64_t split_stride;
+  int64_t ld;
+};
+
+static int gemm_tc_impl(int transa, int transb, int64_t M, int64_t N, int64_t K, const float* a, int64_t lda,
+                        const float* b, int64_t ldb, float* c, int64_t ldc, int accumulate,
+                        GemmPartials* partials_out) {
   std::lock_guard<std::mutex> lock(tc_host().mu);
   if (int rc = tc_setup()) return rc;
   const State& s = state();
@@ -613,15 +623,41 @@ int gemm_tc(int transa, int transb, int64_t M, int64_t N, int64_t K, const float
     default: gemm_tf32x3_kernel<128><<<grid, TC_THREADS, TcConfig<128>::SMEM_BYTES, s.stream>>>(ma, mb, dst, m, n, k, dst_ld, acc_flag, amn, bmn, flag, kb_per_split, split_stride); break;
   }
   B200_LAUNCH_CHECK();
-  if (splits > 1) {
+  if (partials_out) {
+    partials_out->ptr = dst;
+    partials_out->splits = splits;
+    partials_out->split_stride = split_stride;
+    partials_out->ld = dst_ld;
+  } else if (splits > 1) {
     const int64_t total = M * dst_ld;
     int64_t blocks = ceil_div(total / 4, 256);
     if (blocks > (int64_t)s.sm_count * 8) blocks = (int64_t)s.sm_count * 8;
     splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, s.stream>>>(dst, splits, split_stride, c, M, N, dst_ld, ldc, accumulate);
+    B200_LAUNCH_CHECK();
   }
   release(&sa);
   release(&sb);
-  B200_LAUNCH_CHECK();
+  return B200_OK;
+}
+
+int gemm_tc(int transa, int transb, int64_t M, int64_t N, int64_t K, const float* a, int64_t lda,
+            const float* b, int64_t ldb, float* c, int64_t ldc, int accumulate) {
+  // tiny problems: the CUDA-core kernel has less fixed cost
+  if (M * N * K < (int64_t)64 * 64 * 64 && state().gemm_path != 2) return B200_ERR_UNSUPPORTED;
+  return gemm_tc_impl(transa, transb, M, N, K, a, lda, b, ldb, c, ldc, accumulate, nullptr);
+}
+
+// out = op(a).op(b) into `c` (pitch ldc) when one pass suffices, or into the library's
+// partial buffer when the problem was split along K; *where says which.
+int gemm_tc_partials(int transa, int transb, int64_t M, int64_t N, int64_t K, const float* a, int64_t lda,
+                     const float* b, int64_t ldb, float* c, int64_t ldc, const float** ptr, int* splits,
+                     int64_t* split_stride, int64_t* ld) {
+  GemmPartials p;
+  if (int rc = gemm_tc_impl(transa, transb, M, N, K, a, lda, b, ldb, c, ldc, 0, &p)) return rc;
+  *ptr = p.ptr;
+  *splits = p.splits;
+  *split_stride = p.split_stride;
+  *ld = p.ld;
   return B200_OK;
 }
 

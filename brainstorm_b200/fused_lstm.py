@@ -1,0 +1,150 @@
+"""Drop-in fused LSTM layer for networks that run on ``B200Handler``.
+
+``FusedLstmLayerImpl`` subclasses the reference's ``LstmLayerImpl``
+(brainstorm/layers/lstm_layer.py:21) and keeps its ``setup`` untouched, so
+parameter names, order and shapes (:38-55), the twenty internal buffers (:57-87),
+memory layout, initialisers and saved networks are interchangeable with the
+reference layer.  Only ``forward_pass`` / ``backward_pass`` differ: the four input
+projections are one stacked GEMM, and the loop over time is one library call that
+runs, per timestep, one stacked recurrent GEMM and one gate kernel
+(``b200_lstm_forward`` / ``b200_lstm_backward``) instead of 19 / 20 handler calls.
+
+    net.set_handler(B200Handler())
+    fuse_lstm_layers(net)            # swaps the class of every LSTM layer in place
+
+Every buffer the reference layer fills is filled with the same values (to
+rounding: the recurrent contributions of the four gates are summed inside one
+GEMM instead of one after the other).
+"""
+from __future__ import annotations
+
+from brainstorm.layers.lstm_layer import LstmLayerImpl
+from brainstorm.utils import flatten_time, flatten_time_and_features
+
+from ._lib import lib, check
+from .array import B200Array
+from .handler import B200Handler
+
+_ACT = {'sigmoid': 0, 'tanh': 1, 'rel': 2, 'el': 3, 'linear': 4}
+
+
+def _stack(views, shape):
+    """One array over parameter views that lie back to back in memory, or None."""
+    for a, b in zip(views[:-1], views[1:]):
+        if not (a.is_contiguous and b.is_contiguous and a.ptr + 4 * a.size == b.ptr):
+            return None
+    return B200Array(views[0].base, views[0].ptr, shape)
+
+
+def _aligned(h, arr):
+    """arr itself if it starts on a 16-byte boundary, else an aligned copy."""
+    if arr.ptr % 16 == 0:
+        return arr
+    c = B200Array.empty(arr.shape, zero=False)
+    h.copy_to(arr, c)
+    return c
+
+
+class FusedLstmLayerImpl(LstmLayerImpl):
+
+    def _stacks(self, views, in_size):
+        H = self.size
+        (Wz, Wi, Wf, Wo, pi, pf, po, Rz, Ri, Rf, Ro, bz, bi, bf, bo) = views
+        return (_stack([Wz, Wi, Wf, Wo], (4 * H, in_size)), _stack([Rz, Ri, Rf, Ro], (4 * H, H)),
+                _stack([bz, bi, bf, bo], (4 * H,)), _stack([pi, pf, po], (3 * H,)))
+
+    def forward_pass(self, buffers, training_pass=True):
+        h = self.handler
+        x = buffers.inputs.default
+        y = buffers.outputs.default
+        T, B = x.shape[0], x.shape[1]
+        H = self.size
+        flat_x = flatten_time_and_features(x)
+        stacks = self._stacks(buffers.parameters, flat_x.shape[1])
+        hubs = list(buffers.internals)[:10] + [y]
+        if (not isinstance(h, B200Handler) or any(s is None for s in stacks) or
+                not all(a.is_contiguous for a in hubs) or T == 0):
+            self._fused = None
+            return LstmLayerImpl.forward_pass(self, buffers, training_pass)
+        Wst, Rst, bst, pst = stacks
+        (Za, Zb, Ia, Ib, Fa, Fb, Oa, Ob, Ca, Cb) = hubs[:10]
+        xproj = B200Array.empty((T * B, 4 * H), zero=False)
+        h.dot_mm(flat_x, Wst, xproj, transb=True)               # lstm_layer.py:110-113, stacked
+        Rw = _aligned(h, Rst)
+        y_work = B200Array.empty((T + 1, B, H), zero=False)
+        h.copy_to(y[T], y_work[T])                              # context: y[t-1] at t = 0
+        r_work = B200Array.empty((B, 4 * H), zero=False)
+        check(lib.b200_lstm_forward(xproj.ptr, Rw.ptr, bst.ptr, pst.ptr, Za.ptr, Zb.ptr, Ia.ptr, Ib.ptr,
+                                    Fa.ptr, Fb.ptr, Oa.ptr, Ob.ptr, Ca.ptr, Cb.ptr, y.ptr, y_work.ptr,
+                                    r_work.ptr, T, B, H, _ACT[self.activation]))
+        self._fused = (Rw, y_work, r_work)
+
+    def backward_pass(self, buffers):
+        fused = getattr(self, '_fused', None)
+        if fused is None:
+            return LstmLayerImpl.backward_pass(self, buffers)
+        h = self.handler
+        Rw, y_work, r_work = fused
+        x = buffers.inputs.default
+        dx = buffers.input_deltas.default
+        deltas = buffers.output_deltas.default
+        T, B = x.shape[0], x.shape[1]
+        H = self.size
+        flat_x = flatten_time_and_features(x)
+        Wst, _, _, pst = self._stacks(buffers.parameters, flat_x.shape[1])
+        dWst, dRst, dbst, _ = self._stacks(buffers.gradients, flat_x.shape[1])
+        (dpi, dpf, dpo) = list(buffers.gradients)[4:7]
+        (Za, Zb, Ia, Ib, Fa, Fb, Oa, Ob, Ca, Cb,
+         dZa, dZb, dIa, dIb, dFa, dFb, dOa, dOb, dCa, dCb) = buffers.internals
+        if dWst is None or dRst is None or dbst is None or not deltas.is_contiguous:
+            return LstmLayerImpl.backward_pass(self, buffers)
+
+        dG = B200Array.empty((T + 1, B, 4 * H), zero=False)
+        h.fill(dG[T], 0.0)
+        h.fill(dCa, 0.0)                                        # lstm_layer.py:168
+        check(lib.b200_lstm_backward(deltas.ptr, Rw.ptr, pst.ptr, Zb.ptr, Ib.ptr, Fb.ptr, Ob.ptr, Ca.ptr,
+                                     Cb.ptr, dZa.ptr, dZb.ptr, dIa.ptr, dIb.ptr, dFa.ptr, dFb.ptr,
+                                     dOa.ptr, dOb.ptr, dCa.ptr, dCb.ptr, dG.ptr, r_work.ptr, T, B, H,
+                                     _ACT[self.activation]))
+        dGf = dG[:T].reshape((T * B, 4 * H))
+        # input deltas and input-weight gradients (:216-224), four gates at once
+        h.dot_add_mm(dGf, Wst, flatten_time_and_features(dx))
+        h.dot_add_mm(dGf, flat_x, dWst, transa=True)
+        # biases (:226-234)
+        tmp = B200Array.empty((4 * H,), zero=False)
+        h.sum_t(dGf, axis=0, out=tmp)
+        h.add_tt(dbst, tmp, dbst)
+        # recurrent-weight gradients (:253-256); the extra term of :258-261 multiplies
+        # a slice of the reference's temporary that is never written, i.e. zeros
+        if T > 1:
+            h.dot_add_mm(dG[1:T].reshape(((T - 1) * B, 4 * H)),
+                         y_work[:T - 1].reshape(((T - 1) * B, H)), dRst, transa=True)
+        # peepholes (:236-278)
+        dWc = B200Array.empty(dpo.shape, zero=False)
+        prod = B200Array.empty((T * B, H), zero=False)
+        h.mult_tt(flatten_time(Ca[:T]), flatten_time(dOa[:T]), prod)
+        h.sum_t(prod, axis=0, out=dWc)
+        h.add_tt(dpo, dWc, dpo)
+        for d_gate, d_peep in ((dIa, dpi), (dFa, dpf)):
+            if T > 1:
+                p1 = prod[:(T - 1) * B]
+                h.mult_tt(flatten_time(Ca[:T - 1]), flatten_time(d_gate[1:T]), p1)
+                h.sum_t(p1, axis=0, out=dWc)
+                h.add_tt(d_peep, dWc, d_peep)
+            p0 = prod[:B]
+            h.mult_tt(dCa[T], dIa[0], p0)                        # :273-278 (both use dIa[0])
+            h.sum_t(p0, axis=0, out=dWc)
+            h.add_tt(d_peep, dWc, d_peep)
+        self._fused = None
+
+
+def fuse_lstm_layers(net):
+    """Swap every LSTM layer of ``net`` for the fused implementation, in place.
+    Returns the names of the layers that were swapped."""
+    swapped = []
+    for name, layer in net.layers.items():
+        if type(layer) is LstmLayerImpl:
+            layer.__class__ = FusedLstmLayerImpl
+            layer._fused = None
+            swapped.append(name)
+    return swapped

@@ -168,6 +168,23 @@ int b200_nonfinite_flag(const float* a, int64_t rows, int64_t cols, int64_t ld, 
 int b200_dot_mm(const float* a, const float* b, float* out, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldo, int transa, int transb);
 int b200_dot_add_mm(const float* a, const float* b, float* out, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldo, int transa, int transb);
 
+/* ---- fused LSTM sequence passes: the per-timestep body of
+ *      LstmLayerImpl.forward_pass (brainstorm/layers/lstm_layer.py:115-145) and
+ *      LstmLayerImpl.backward_pass (:171-205).  Per timestep: one stacked recurrent
+ *      GEMM on the tensor cores + one gate kernel; the loop over time runs inside
+ *      the library.  Buffers are the layer's own (T+1, B, H) arrays (context slot
+ *      at index T); gate order is z, i, f, o as in the parameter vector (:39-55).
+ *      act: 0 sigmoid, 1 tanh, 2 rel, 3 el, 4 linear.  xproj (T*B, 4H) holds the
+ *      input projections; y_work (T+1, B, H), dg_work (T+1, B, 4H) and r_work
+ *      (B, 4H) are 16-byte aligned work arrays of the caller. ------------------ */
+int b200_lstm_forward(const float* xproj, const float* r_stack, const float* bias, const float* peep,
+                      float* za, float* zb, float* ia, float* ib, float* fa, float* fb, float* oa, float* ob,
+                      float* ca, float* cb, float* y, float* y_work, float* r_work, int T, int B, int H, int act);
+int b200_lstm_backward(const float* deltas, const float* r_stack, const float* peep,
+                       const float* zb, const float* ib, const float* fb, const float* ob, const float* ca, const float* cb,
+                       float* dza, float* dzb, float* dia, float* dib, float* dfa, float* dfb, float* doa, float* dob,
+                       float* dca, float* dcb, float* dg_work, float* r_work, int T, int B, int H, int act);
+
 /* ---- random: generate_probability_mask :507, fill_gaussian :494;
  *      numpy_handler.py:199,193.  Device-side Philox4x32-10 streams addressed by
  *      (seed, offset); the host-RNG parity mode of the Python handler does not

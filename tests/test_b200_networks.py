@@ -8,7 +8,7 @@ from conftest import needs_reference
 pytestmark = [pytest.mark.gpu, needs_reference]
 
 
-def _pair(builder, **kw):
+def _pair(builder, fused=False, **kw):
     import brainstorm as bs
     from brainstorm.handlers import NumpyHandler
     from brainstorm_b200 import B200Handler
@@ -16,6 +16,9 @@ def _pair(builder, **kw):
     net_cpu.set_handler(NumpyHandler(np.float32, seed=77))
     net_gpu, _, _ = builder(**kw)
     net_gpu.set_handler(B200Handler(seed=77, rng_mode='host'))
+    if fused:
+        from brainstorm_b200.fused_lstm import fuse_lstm_layers
+        assert len(fuse_lstm_layers(net_gpu)) == 2
     p_cpu = net_cpu.get('parameters')
     p_gpu = net_gpu.get('parameters')
     assert np.array_equal(p_cpu, p_gpu)
@@ -37,10 +40,10 @@ def _close_l2(got, want, rtol, what):
     assert err <= rtol * ref, '%s: L2 err %.3g vs norm %.3g' % (what, err, ref)
 
 
-def _check_training(builder, steps, rtol, compare=None, **kw):
+def _check_training(builder, steps, rtol, compare=None, fused=False, **kw):
     compare = compare or _close
     from brainstorm_b200.workloads import train_steps
-    net_cpu, net_gpu, data, stepper = _pair(builder, **kw)
+    net_cpu, net_gpu, data, stepper = _pair(builder, fused=fused, **kw)
     # one forward/backward: loss, every gradient
     for net in (net_cpu, net_gpu):
         net.provide_external_data(data)
@@ -71,6 +74,48 @@ def test_lstm_two_layers_sgd():
 def test_lstm_aligned_sizes_use_tensor_cores():
     from brainstorm_b200 import workloads
     _check_training(workloads.lstm, steps=2, rtol=2e-4, time=6, batch=64, vocab=48, hidden=128)
+
+
+@pytest.mark.parametrize('shape', [dict(time=7, batch=9, vocab=23, hidden=32),
+                                   dict(time=6, batch=64, vocab=48, hidden=128),
+                                   dict(time=1, batch=5, vocab=7, hidden=12),
+                                   dict(time=12, batch=128, vocab=205, hidden=200)],
+                         ids=['ragged', 'aligned', 'one-step', 'wide'])
+def test_fused_lstm_layer_matches_reference_layer(shape):
+    """The fused layer on the GPU against the reference's own LstmLayerImpl on
+    NumpyHandler: loss, every gradient, parameters after SGD steps -- and every
+    one of the twenty internal buffers plus outputs and input deltas."""
+    from brainstorm_b200 import workloads
+    net_cpu, net_gpu = _check_training(workloads.lstm, steps=2, rtol=2e-4, fused=True, **shape)
+    for net in (net_cpu, net_gpu):
+        net.forward_pass(training_pass=True)
+        net.backward_pass()
+    for lname in net_cpu.layers:
+        if not lname.startswith('Lstm'):
+            continue
+        T = shape['time']
+        for kind in ('internals', 'outputs', 'input_deltas'):
+            for bname in net_cpu.buffer[lname][kind].keys():
+                path = '%s.%s.%s' % (lname, kind, bname)
+                c, g = net_cpu.get(path), net_gpu.get(path)
+                if c.shape[0] == T + 1:    # the context slot is not part of the pass
+                    c, g = c[:T], g[:T]
+                _close(g, c, 2e-4, path)
+
+
+def test_fused_lstm_carries_context_between_calls():
+    """Truncated BPTT: forward passes with context hand y and the cell state from
+    one chunk to the next (network.py:405-428); the fused layer must read them."""
+    from brainstorm_b200 import workloads
+    net_cpu, net_gpu, data, _ = _pair(workloads.lstm, fused=True, time=5, batch=6, vocab=11, hidden=16)
+    outs = []
+    for net in (net_cpu, net_gpu):
+        net.provide_external_data(data)
+        net.forward_pass(training_pass=True)
+        ctx = net.get_context()
+        net.forward_pass(training_pass=True, context=ctx)
+        outs.append(net.get('Output_projection.outputs.default'))
+    _close(outs[1], outs[0], 1e-4, 'outputs of the second chunk')
 
 
 def test_highway_batchnorm_stack():
