@@ -239,6 +239,61 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+# ------------------------------------------------------------------ LSTM training step
+def lstm_training(H, world, rank, steps, barrier, lib, check):
+    """Second half of the metric: training sequences per second of the character
+    LSTM (time 100, batch 128 per GPU, 205 symbols, 2 x 1000 units, SoftmaxCE, SGD),
+    run through the reference's unchanged Network / SgdStepper on this handler with
+    the fused LSTM layer.  Every step uploads its batch from host memory and reads
+    the loss back, as Trainer does."""
+    ref = os.path.join(ROOT, 'baseline', '_ref')
+    if os.path.isdir(os.path.join(ref, 'brainstorm')) and ref not in sys.path:
+        sys.path.insert(0, ref)
+    try:
+        import brainstorm  # noqa: F401
+    except Exception as e:
+        return {'unavailable': 'brainstorm (the caller of the handler) is not importable: %s' % e}
+    from brainstorm_b200 import workloads
+    from brainstorm_b200.fused_lstm import fuse_lstm_layers
+    T, B = 100, 128
+    net, data, stepper = workloads.lstm(time=T, batch=B, data_seed=rank)
+    net.set_handler(H)
+    fuse_lstm_layers(net)
+    if world > 1:
+        from brainstorm_b200.parallel import Comm, data_parallel
+        data_parallel(net, Comm())
+    st = stepper()
+    st.start(net)
+
+    def step():
+        net.provide_external_data(data)
+        st.run()
+        return float(net.get_loss_values()['total_loss'])
+
+    for _ in range(3):
+        loss = step()
+    barrier()
+    l0 = lib.b200_launch_count()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        loss = step()
+    barrier()
+    dt = (time.perf_counter() - t0) / steps
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        tt = torch.tensor([dt], device='cuda')
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        dt = float(tt.item())
+    return {'sequences_per_s': round(world * B / dt, 1), 'ms_per_step': round(dt * 1e3, 3),
+            'time_steps': T, 'batch_per_gpu': B, 'global_batch': world * B, 'hidden': 1000, 'layers': 2,
+            'steps': steps, 'loss': round(loss, 4),
+            'gpu_launches_per_step': int((lib.b200_launch_count() - l0) // steps),
+            'h2d_bytes_per_step': int(sum(v.nbytes for v in data.values())),
+            'timing': 'host wall clock around whole steps (each step ends with the loss read-back), max over ranks',
+            'parallelism': 'dp%d, gradient all-reduce (avg) of %d parameters' % (world, net.buffer.parameters.size)}
+
+
 # ------------------------------------------------------------------ GPU arm
 def run_b200(args):
     world = int(os.environ.get('WORLD_SIZE', '1'))
@@ -369,6 +424,8 @@ def run_b200(args):
         e2e_s = float(tt.item())
     e2e_value = world * step_bytes / e2e_s / 1e9
 
+    lstm = lstm_training(H, world, rank, max(3, min(args.steps, 10)), barrier, lib, check)
+
     if rank == 0:
         peaks, peak_src = None, 'fallback'
         try:
@@ -410,6 +467,7 @@ def run_b200(args):
                          'peak': peak, 'peak_source': peak_src, 'unit': 'GB/s',
                          'frac': round(achieved / peak, 4), 'traffic': traffic},
             'cpu_baseline': cpu,
+            'lstm': lstm,
             'ops': ops,
         }
         print(json.dumps(line))

@@ -521,8 +521,17 @@ class B200Handler(Handler):
         self.copy_to(a, c)
         return c
 
+    def set_comm(self, comm, axis0_reduce='local'):
+        """Complete ``sum_t(axis=0)`` across batch shards: ``'sum'`` / ``'avg'``
+        all-reduce the result over ``comm`` (brainstorm_b200.parallel.Comm),
+        ``'local'`` exchanges nothing."""
+        if axis0_reduce not in ('local', 'sum', 'avg'):
+            raise ValueError("axis0_reduce must be 'local', 'sum' or 'avg'")
+        self._comm = comm
+        self.axis0_reduce = axis0_reduce
+
     def _allreduce_axis0(self, dst):
-        raise NotImplementedError
+        self._comm.allreduce(dst, self.axis0_reduce)
 
 
 _default = [None]
