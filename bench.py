@@ -328,6 +328,15 @@ def run_b200(args):
         check(lib.b200_event_elapsed_ms(e0, e1, ctypes.byref(ms)))
         return ms.value
 
+    if args.only == 'gemm':
+        return run_gemm(args, H, lib, check, new_event, elapsed)
+    if args.only == 'lstm':
+        lstm = lstm_training(H, world, rank, max(1, args.steps), barrier, lib, check)
+        if rank == 0:
+            print(json.dumps({'metric': 'lstm_train_sequences_per_s', 'value': lstm.get('sequences_per_s'),
+                              'unit': 'sequences/s', 'n_gpus': world, 'lstm': lstm}))
+        return
+    ROWS = args.rows
     # ---- operands: page-locked host copies (for e2e) and device-resident arrays
     host = host_inputs(ROWS, COLS, SEED + rank, alloc=H.pinned_empty)
     t = {k: H.create_from_numpy(v) for k, v in host.items()}
@@ -397,6 +406,13 @@ def run_b200(args):
     ops = {name: {'ms': round(ms, 4), 'gbs': round(nbytes[name] / (ms * 1e-3) / 1e9, 1)}
            for name, ms in op_ms.items()}
 
+    if args.only == 'suite':
+        if rank == 0:
+            print(json.dumps({'metric': METRIC, 'value': round(value, 1), 'unit': UNIT, 'n_gpus': world,
+                              'steps': args.steps, 'ms_per_step': round(ms_per_step, 4),
+                              'config': {'workload': 'handler op suite only, (%d, %d)' % (ROWS, COLS)},
+                              'gpu_launches': int(launches), 'ops': ops}))
+        return
     # ---- end to end: host buffers in, results out, every step
     e2e_steps = max(1, min(args.steps, 3))
     results = [np.empty((1, COLS), np.float32), np.empty((ROWS, 1), np.float32),
@@ -455,7 +471,7 @@ def run_b200(args):
             'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32',
             'data': 'synthetic (seeded block tiled down the rows)',
             'config': {'workload': 'handler op suite (27 ops), fp32 (%d, %d) operands per GPU, '
-                                   '1 GiB each' % (ROWS, COLS),
+                                   '%.3g GiB each' % (ROWS, COLS, ROWS * COLS * 4 / 2.0 ** 30),
                        'rows_per_gpu': ROWS, 'cols': COLS, 'seed': SEED,
                        'l2': 'operands (1 GiB) exceed L2 (126 MB); no flush needed',
                        'sharding': 'rows; axis-0 sum all-reduced over NCCL' if world > 1 else 'single GPU'},
@@ -475,12 +491,43 @@ def run_b200(args):
         dist.destroy_process_group()
 
 
+def run_gemm(args, H, lib, check, new_event, elapsed):
+    """--only gemm: times dot_mm (a . b^T) at one shape on the tensor-core path and
+    on the CUDA-core path; used for the ncu captures of the GEMM kernel."""
+    M, N, K = [int(v) for v in args.gemm.split(',')]
+    rs = np.random.RandomState(SEED)
+    a = H.create_from_numpy(rs.uniform(-1, 1, (M, K)).astype(np.float32))
+    b = H.create_from_numpy(rs.uniform(-1, 1, (N, K)).astype(np.float32))
+    out = H.zeros((M, N))
+    res = {}
+    for name, path in (('tensor_core_tf32x3', 2), ('cuda_core_fp32', 1)):
+        check(lib.b200_set_tuning(2, path))
+        for _ in range(3):
+            H.dot_mm(a, b, out, transb=True)
+        e0, e1 = new_event(), new_event()
+        reps = args.steps if path == 2 else max(1, args.steps // 4)
+        check(lib.b200_event_record(e0))
+        for _ in range(reps):
+            H.dot_mm(a, b, out, transb=True)
+        check(lib.b200_event_record(e1))
+        ms = elapsed(e0, e1) / reps
+        res[name] = {'ms': round(ms, 4), 'tflops': round(2.0 * M * N * K / ms / 1e9, 1)}
+    check(lib.b200_set_tuning(2, 0))
+    print(json.dumps({'metric': 'dot_mm_fp32_tflops', 'value': res['tensor_core_tf32x3']['tflops'],
+                      'unit': 'TFLOP/s', 'config': {'workload': 'dot_mm NT %dx%dx%d' % (M, N, K)},
+                      'paths': res}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
     ap.add_argument('--steps', type=int, default=30)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
+    ap.add_argument('--only', default='all', choices=['all', 'suite', 'gemm', 'lstm'],
+                    help='suite: device-resident op suite only; gemm: one dot_mm shape (for profiling)')
+    ap.add_argument('--rows', type=int, default=ROWS, help='rows of the op-suite operands (default 65536)')
+    ap.add_argument('--gemm', default='8192,4096,4096', help='M,N,K for --only gemm')
     args = ap.parse_args()
     if args.impl == 'reference':
         run_reference(args)
