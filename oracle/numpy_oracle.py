@@ -312,3 +312,80 @@ def op_suite_inputs(rows, cols, seed):
     d['div'] = (u((rows, cols), 0.5, 4.0) * sign).astype(f32)
     d['labels'] = rs.randint(0, cols, size=(rows, 1)).astype(np.int32)
     return d
+
+
+# --------------------------------------------------------------------------
+# Whole-sequence LSTM passes, restated from lstm_layer.py with the oracle's ops
+# in the reference's own order (so the results are bit-identical to running
+# LstmLayerImpl on NumpyHandler).  `p` holds the fifteen parameters by name,
+# `f` the ten forward internals + 'y' as (T+1, B, H) arrays (context in slot T).
+# --------------------------------------------------------------------------
+LSTM_PARAMS = ('Wz', 'Wi', 'Wf', 'Wo', 'pi', 'pf', 'po', 'Rz', 'Ri', 'Rf', 'Ro', 'bz', 'bi', 'bf', 'bo')
+LSTM_FORWARD = ('Za', 'Zb', 'Ia', 'Ib', 'Fa', 'Fb', 'Oa', 'Ob', 'Ca', 'Cb')
+LSTM_BACKWARD = ('dZa', 'dZb', 'dIa', 'dIb', 'dFa', 'dFb', 'dOa', 'dOb', 'dCa', 'dCb')
+
+
+def lstm_forward(O, p, x, f, activation='tanh'):
+    """lstm_layer.py:90-145."""
+    T, B = x.shape[0], x.shape[1]
+    flat_x = x.reshape(T * B, -1)
+    for g in 'zifo':                                     # :110-113
+        O.dot_mm(flat_x, p['W' + g], f[g.upper() + 'a'][:T].reshape(T * B, -1), transb=True)
+    y = f['y']
+    for t in range(T):
+        for g in 'zifo':                                 # :117,:122,:128,:138
+            O.dot_add_mm(y[t - 1], p['R' + g], f[g.upper() + 'a'][t], transb=True)
+        O.lstm_step_forward(f['Za'][t], f['Ia'][t], f['Fa'][t], f['Oa'][t], f['Ca'][t - 1],
+                            p['bz'], p['bi'], p['bf'], p['bo'], p['pi'], p['pf'], p['po'],
+                            f['Zb'][t], f['Ib'][t], f['Fb'][t], f['Ob'][t], f['Ca'][t], f['Cb'][t],
+                            y[t], activation)
+
+
+def lstm_backward(O, p, x, f, deltas, d, grads, dx, activation='tanh'):
+    """lstm_layer.py:147-278.  `d` holds the ten backward internals (zero-filled,
+    (T+1, B, H)), `grads` the fifteen gradients (accumulated into), `dx` the input
+    deltas (accumulated into)."""
+    T, B = x.shape[0], x.shape[1]
+    H = f['y'].shape[2]
+    dy = np.zeros_like(f['y'])
+    d['dCa'][...] = 0
+    for t in range(T - 1, -1, -1):
+        O.copy_to(deltas[t], dy[t])                                       # :173
+        for g in 'ifoz':                                                  # :174-177
+            O.dot_add_mm(d['d' + g.upper() + 'a'][t + 1], p['R' + g], dy[t])
+        O.lstm_step_backward(dy[t], d['dIa'][t + 1], d['dFa'][t + 1], d['dCa'][t + 1], f['Fb'][t + 1],
+                             p['pi'], p['pf'], p['po'], f['Za'][t], f['Zb'][t], f['Ia'][t], f['Ib'][t],
+                             f['Fa'][t], f['Fb'][t], f['Oa'][t], f['Ob'][t], f['Ca'][t], f['Cb'][t],
+                             f['Ca'][t - 1], d['dZa'][t], d['dZb'][t], d['dIa'][t], d['dIb'][t],
+                             d['dFa'][t], d['dFb'][t], d['dOa'][t], d['dOb'][t], d['dCa'][t], d['dCb'][t],
+                             activation)
+    flat_x = x.reshape(T * B, -1)
+    flat_dx = dx.reshape(T * B, -1)
+    fl = lambda a: a.reshape(a.shape[0] * a.shape[1], -1)
+    for g in 'ifoz':                                                      # :216-224
+        O.dot_add_mm(fl(d['d' + g.upper() + 'a'][:T]), p['W' + g], flat_dx)
+    for g in 'ifoz':
+        O.dot_add_mm(fl(d['d' + g.upper() + 'a'][:T]), flat_x, grads['W' + g], transa=True)
+    tmp = np.zeros((H,), x.dtype)
+    for g in 'ifoz':                                                      # :226-234
+        O.sum_t(fl(d['d' + g.upper() + 'a'][:T]), 0, tmp)
+        O.add_tt(grads['b' + g], tmp, grads['b' + g])
+    y, Ca = f['y'], f['Ca']
+    big = np.zeros((T * B, H), x.dtype)
+    dWc = np.zeros((1, H), x.dtype)
+    O.mult_tt(fl(Ca[:T]), fl(d['dOa'][:T]), big)                          # :244-246
+    O.sum_t(big, 0, dWc)
+    O.add_tt(grads['po'], dWc, grads['po'])
+    for g in 'ifoz':                                                      # :253-261
+        O.dot_add_mm(fl(d['d' + g.upper() + 'a'][1:T]), fl(y[:T - 1]), grads['R' + g], transa=True)
+        O.dot_add_mm(d['d' + g.upper() + 'a'][0], dy[-1], grads['R' + g], transa=True)
+    part = np.zeros(((T - 1) * B, H), x.dtype)
+    for g in 'if':                                                        # :264-270
+        O.mult_tt(fl(Ca[:T - 1]), fl(d['d' + g.upper() + 'a'][1:T]), part)
+        O.sum_t(part, 0, dWc)
+        O.add_tt(grads['p' + g], dWc, grads['p' + g])
+    one = np.zeros((B, H), x.dtype)
+    for g in 'if':                                                        # :272-278 (both use dIa[0])
+        O.mult_tt(d['dCa'][-1], d['dIa'][0], one)
+        O.sum_t(one, 0, dWc)
+        O.add_tt(grads['p' + g], dWc, grads['p' + g])
