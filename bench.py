@@ -294,6 +294,43 @@ def lstm_training(H, world, rank, steps, barrier, lib, check):
             'parallelism': 'dp%d, gradient all-reduce (avg) of %d parameters' % (world, net.buffer.parameters.size)}
 
 
+def other_training_configs(H, rank, lib):
+    """Single-GPU step times of the two other training workloads (extra keys of
+    the bench line): the MNIST-style MLP (batch 100, momentum SGD) and the Highway +
+    BatchNorm stack (batch 8192, width 4096, 10 blocks)."""
+    try:
+        import brainstorm  # noqa: F401
+    except Exception as e:
+        return {'unavailable': 'brainstorm is not importable: %s' % e}
+    from brainstorm_b200 import workloads
+    out = {}
+    for name, build, steps in (('mlp', workloads.mlp, 50), ('highway_bn', workloads.highway_bn, 3)):
+        net, data, stepper = build()
+        net.set_handler(H)
+        st = stepper()
+        st.start(net)
+
+        def step():
+            net.provide_external_data(data)
+            st.run()
+            return float(net.get_loss_values()['total_loss'])
+
+        for _ in range(3):
+            step()
+        H.synchronize()
+        l0 = lib.b200_launch_count()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            step()
+        H.synchronize()
+        dt = (time.perf_counter() - t0) / steps
+        batch = data['default'].shape[1]
+        out[name] = {'samples_per_s': round(batch / dt, 1), 'ms_per_step': round(dt * 1e3, 3), 'batch': batch,
+                     'gpu_launches_per_step': int((lib.b200_launch_count() - l0) // steps)}
+        del net
+    return out
+
+
 # ------------------------------------------------------------------ GPU arm
 def run_b200(args):
     world = int(os.environ.get('WORLD_SIZE', '1'))
@@ -441,6 +478,8 @@ def run_b200(args):
     e2e_value = world * step_bytes / e2e_s / 1e9
 
     lstm = lstm_training(H, world, rank, max(3, min(args.steps, 10)), barrier, lib, check)
+    del t, suite
+    others = other_training_configs(H, rank, lib) if world == 1 else None
 
     if rank == 0:
         peaks, peak_src = None, 'fallback'
@@ -484,6 +523,7 @@ def run_b200(args):
                          'frac': round(achieved / peak, 4), 'traffic': traffic},
             'cpu_baseline': cpu,
             'lstm': lstm,
+            'other_training': others,
             'ops': ops,
         }
         print(json.dumps(line))

@@ -28,9 +28,11 @@ struct Params {
 
 __device__ __forceinline__ float sigmoid_f(float x) {
   // sign-split stable form: 1/(1+exp(-x)) for x >= 0, exp(x)/(1+exp(x)) for x < 0
+  // One correctly rounded reciprocal instead of an IEEE division: r = 1/(1+e) is the
+  // x >= 0 result to 0.5 ulp; e*r differs from e/(1+e) by at most 1 ulp more.
   const float e = expf(-fabsf(x));
-  const float d = 1.0f + e;
-  return (x >= 0.0f) ? __fdiv_rn(1.0f, d) : __fdiv_rn(e, d);
+  const float r = __frcp_rn(1.0f + e);
+  return (x >= 0.0f) ? r : __fmul_rn(e, r);
 }
 __device__ __forceinline__ float sign_f(float x) {
   return (x > 0.0f) ? 1.0f : ((x < 0.0f) ? -1.0f : x);  // sign(+-0) = +-0, NaN stays NaN
@@ -349,31 +351,37 @@ static int launch_mv(const float* m, const float* v, float* out, int64_t rows, i
 
 // ---- labels ---------------------------------------------------------------------
 // out[r, c] = (c == int(v[r])) ? 1 : 0 ; every element of out is written once.
-__global__ void __launch_bounds__(256)
-binarize_kernel(const float* v, int64_t ldv, float* out, int64_t rows, int64_t cols, int64_t ldo,
-                int vec, int stream) {
-  const int64_t rstride = gridDim.y;
-  if (vec) {
-    const int64_t cols4 = cols >> 2;
-    for (int64_t r = blockIdx.y; r < rows; r += rstride) {
-      const int lab = (int)v[r * ldv];
-      float* orow = out + r * ldo;
-      for (int64_t c4 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c4 < cols4;
-           c4 += (int64_t)gridDim.x * blockDim.x) {
-        const int c = (int)(c4 << 2);
-        const float4 o = make_float4(lab == c ? 1.f : 0.f, lab == c + 1 ? 1.f : 0.f,
-                                     lab == c + 2 ? 1.f : 0.f, lab == c + 3 ? 1.f : 0.f);
-        if (stream) __stcs(reinterpret_cast<float4*>(orow) + c4, o);
-        else reinterpret_cast<float4*>(orow)[c4] = o;
-      }
+// Flat grid-stride over float4 groups (or single elements), four stores in flight
+// per thread; the label of a row is a broadcast load that stays in L1.
+template <bool VEC, bool STREAM>
+__global__ void __launch_bounds__(1024)
+binarize_kernel(const float* v, int64_t ldv, float* out, int64_t rows, int64_t cols, int64_t ldo) {
+  const int64_t per_row = VEC ? (cols >> 2) : cols;
+  const int64_t total = rows * per_row;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t base = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; base < total;
+       base += stride * EW_UNROLL) {
+    int lab[EW_UNROLL];
+    int64_t r[EW_UNROLL], g[EW_UNROLL];
+#pragma unroll
+    for (int u = 0; u < EW_UNROLL; ++u) {
+      const int64_t i = base + u * stride;
+      r[u] = i / per_row;
+      g[u] = i - r[u] * per_row;
+      lab[u] = (i < total) ? (int)v[r[u] * ldv] : -1;
     }
-  } else {
-    for (int64_t r = blockIdx.y; r < rows; r += rstride) {
-      const int lab = (int)v[r * ldv];
-      float* orow = out + r * ldo;
-      for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < cols;
-           c += (int64_t)gridDim.x * blockDim.x)
-        orow[c] = (lab == (int)c) ? 1.f : 0.f;
+#pragma unroll
+    for (int u = 0; u < EW_UNROLL; ++u) {
+      const int64_t i = base + u * stride;
+      if (i >= total) continue;
+      if (VEC) {
+        const int c = (int)(g[u] << 2);
+        st4<STREAM>(out + r[u] * ldo + c,
+                    make_float4(lab[u] == c ? 1.f : 0.f, lab[u] == c + 1 ? 1.f : 0.f,
+                                lab[u] == c + 2 ? 1.f : 0.f, lab[u] == c + 3 ? 1.f : 0.f));
+      } else {
+        st1<STREAM>(out + r[u] * ldo + g[u], lab[u] == (int)g[u] ? 1.f : 0.f);
+      }
     }
   }
 }
@@ -526,16 +534,18 @@ B200_API int b200_binarize_v(const float* v, int64_t ldv, float* out, int64_t ro
   if (rows * cols == 0) return B200_OK;
   B200_REQUIRE(v && out && ldo >= cols && ldv >= 1, "bad operand");
   const State& s = state();
-  const int vec = (cols % 4 == 0) && aligned16(out) && (ldo % 4 == 0);
-  const int64_t per_row = vec ? cols / 4 : cols;
-  const int threads = per_row >= 256 ? 256 : (per_row >= 128 ? 128 : (per_row >= 64 ? 64 : 32));
-  int64_t gx = ceil_div(per_row, threads);
-  if (gx > 64) gx = 64;
-  int64_t gy = ceil_div((int64_t)s.sm_count * 8 * 256 / threads, gx);
-  if (gy > rows) gy = rows;
-  if (gy > 65535) gy = 65535;
-  binarize_kernel<<<dim3((unsigned)gx, (unsigned)gy), threads, 0, s.stream>>>(
-      v, ldv, out, rows, cols, ldo, vec, rows * cols >= STREAM_MIN_ELEMS);
+  const bool vec = (cols % 4 == 0) && aligned16(out) && (ldo % 4 == 0);
+  const bool stream = rows * cols >= STREAM_MIN_ELEMS;
+  const int64_t total = rows * (vec ? cols / 4 : cols);
+  const int threads = s.ew_threads;
+  const int grid = ew_grid(total, threads);
+  if (vec) {
+    if (stream) binarize_kernel<true, true><<<grid, threads, 0, s.stream>>>(v, ldv, out, rows, cols, ldo);
+    else binarize_kernel<true, false><<<grid, threads, 0, s.stream>>>(v, ldv, out, rows, cols, ldo);
+  } else {
+    if (stream) binarize_kernel<false, true><<<grid, threads, 0, s.stream>>>(v, ldv, out, rows, cols, ldo);
+    else binarize_kernel<false, false><<<grid, threads, 0, s.stream>>>(v, ldv, out, rows, cols, ldo);
+  }
   B200_LAUNCH_CHECK();
   return B200_OK;
 }

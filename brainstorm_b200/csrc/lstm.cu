@@ -25,8 +25,8 @@ enum { ACT_SIGMOID = 0, ACT_TANH = 1, ACT_REL = 2, ACT_EL = 3, ACT_LINEAR = 4 };
 
 __device__ __forceinline__ float sigmoid_dev(float x) {
   const float e = expf(-fabsf(x));
-  const float d = 1.0f + e;
-  return (x >= 0.0f) ? __fdiv_rn(1.0f, d) : __fdiv_rn(e, d);
+  const float r = __frcp_rn(1.0f + e);
+  return (x >= 0.0f) ? r : __fmul_rn(e, r);
 }
 __device__ __forceinline__ float act_fwd(int act, float x) {
   switch (act) {

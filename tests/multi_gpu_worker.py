@@ -1,0 +1,59 @@
+"""Worker of tests/test_multi_gpu.py: one rank per GPU (torch.distributed.run).
+Each rank trains on its batch shard with B200Handler + data_parallel; rank 0 checks
+the result against the single-process run of the reference stack on NumpyHandler
+with the whole batch."""
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+for p in (ROOT, os.path.join(ROOT, 'baseline', '_ref')):
+    sys.path.insert(0, p)
+
+
+def main():
+    import torch
+    import torch.distributed as dist
+    local = int(os.environ['LOCAL_RANK'])
+    torch.cuda.set_device(local)
+    dist.init_process_group('nccl', device_id=torch.device('cuda', local))
+    rank, world = dist.get_rank(), dist.get_world_size()
+    from brainstorm.handlers import NumpyHandler
+    from brainstorm_b200 import B200Handler, workloads
+    from brainstorm_b200.fused_lstm import fuse_lstm_layers
+    from brainstorm_b200.parallel import Comm, data_parallel, shard_batch
+    from brainstorm_b200.workloads import train_steps
+    H = B200Handler(seed=3, device=local)
+    ok = True
+    for which, build, mode in (
+            ('highway_bn', lambda: workloads.highway_bn(batch=32 * world, width=64, classes=7, blocks=2), 'avg'),
+            ('lstm', lambda: workloads.lstm(time=6, batch=16 * world, vocab=20, hidden=32), 'local')):
+        net, data, stepper = build()
+        net.set_handler(H)
+        if which == 'lstm':
+            fuse_lstm_layers(net)
+        data_parallel(net, Comm(), axis0_reduce=mode)
+        losses = train_steps(net, shard_batch(data, rank, world), stepper(), 3)
+        params = net.get('parameters')
+        gathered = [None] * world
+        dist.all_gather_object(gathered, (params, losses))
+        if rank == 0:
+            ref, rdata, rstepper = build()
+            ref.set_handler(NumpyHandler(np.float32))
+            rl = train_steps(ref, rdata, rstepper(), 3)
+            want = ref.get('parameters')
+            for r, (p, l) in enumerate(gathered):
+                assert np.array_equal(p, gathered[0][0]), '%s: replicas diverged on rank %d' % (which, r)
+            scale = np.abs(want).max()
+            err = np.abs(params - want).max()
+            mean_loss = np.mean([g[1] for g in gathered], axis=0)
+            print('%s: param err %.3g (scale %.3g), loss %s vs %s' % (which, err, scale, mean_loss, rl))
+            ok = ok and err <= 1e-4 * scale and np.allclose(mean_loss, rl, rtol=1e-4)
+    if rank == 0:
+        print('MULTI_GPU_OK' if ok else 'MULTI_GPU_MISMATCH')
+    dist.destroy_process_group()
+
+
+if __name__ == '__main__':
+    main()
