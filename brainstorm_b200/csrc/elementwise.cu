@@ -259,16 +259,18 @@ static int launch_ew(const float* i0, const float* i1, const float* i2, float* o
 // ACC forms also read out.  Vector form: a thread owns one float4 column group
 // and walks down the rows, so a row vector is loaded once per thread.
 template <class F, bool COL, bool STREAM>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 mv_vec(const float* m, const float* v, float* out, int64_t rows, int cols4, int64_t ldm, int64_t ldo,
        Params p) {
+  // blockDim = (column groups, row lanes); a thread keeps its column group and
+  // walks down the rows, four rows in flight.
   const int c4 = blockIdx.x * blockDim.x + threadIdx.x;
   if (c4 >= cols4) return;
   float4 vr = make_float4(0.f, 0.f, 0.f, 0.f);
   if (!COL) vr = *reinterpret_cast<const float4*>(v + 4 * (int64_t)c4);
   const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-  const int64_t rstride = gridDim.y;
-  for (int64_t r0 = blockIdx.y; r0 < rows; r0 += rstride * EW_UNROLL) {
+  const int64_t rstride = (int64_t)gridDim.y * blockDim.y;
+  for (int64_t r0 = (int64_t)blockIdx.y * blockDim.y + threadIdx.y; r0 < rows; r0 += rstride * EW_UNROLL) {
     float4 a[EW_UNROLL], c[EW_UNROLL];
     float vc[EW_UNROLL];
 #pragma unroll
@@ -322,11 +324,14 @@ static int launch_mv(const float* m, const float* v, float* out, int64_t rows, i
                    cols < ((int64_t)1 << 31);
   if (vec) {
     const int cols4 = (int)(cols / 4);
-    const int threads = cols4 >= 256 ? 256 : (cols4 >= 128 ? 128 : (cols4 >= 64 ? 64 : 32));
-    const int gx = (int)ceil_div(cols4, threads);
-    int64_t want = (int64_t)s.sm_count * s.ew_blocks_per_sm * 256 / threads;
-    int64_t gy = ceil_div(want, gx);
-    const int64_t gy_max = ceil_div(rows, EW_UNROLL);
+    const int tx = cols4 >= 256 ? 256 : (cols4 >= 128 ? 128 : (cols4 >= 64 ? 64 : 32));
+    int ty = s.ew_threads / tx;
+    if (ty < 1) ty = 1;
+    while (ty > 1 && (int64_t)ty * EW_UNROLL > rows) ty >>= 1;
+    const dim3 threads(tx, ty);
+    const int gx = (int)ceil_div(cols4, tx);
+    int64_t gy = ceil_div((int64_t)s.sm_count * s.ew_blocks_per_sm, gx);
+    const int64_t gy_max = ceil_div(rows, (int64_t)ty * EW_UNROLL);
     if (gy > gy_max) gy = gy_max;
     if (gy > 65535) gy = 65535;
     if (gy < 1) gy = 1;
@@ -351,37 +356,31 @@ static int launch_mv(const float* m, const float* v, float* out, int64_t rows, i
 
 // ---- labels ---------------------------------------------------------------------
 // out[r, c] = (c == int(v[r])) ? 1 : 0 ; every element of out is written once.
-// Flat grid-stride over float4 groups (or single elements), four stores in flight
-// per thread; the label of a row is a broadcast load that stays in L1.
+// A thread owns one float4 column group (or one column) and walks down the rows
+// eight at a time: the eight labels are fetched first (broadcast loads), then the
+// eight stores are issued back to back, so no store waits on a label.
+constexpr int BIN_ROWS = 8;
 template <bool VEC, bool STREAM>
-__global__ void __launch_bounds__(1024)
+__global__ void __launch_bounds__(256)
 binarize_kernel(const float* v, int64_t ldv, float* out, int64_t rows, int64_t cols, int64_t ldo) {
   const int64_t per_row = VEC ? (cols >> 2) : cols;
-  const int64_t total = rows * per_row;
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t base = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; base < total;
-       base += stride * EW_UNROLL) {
-    int lab[EW_UNROLL];
-    int64_t r[EW_UNROLL], g[EW_UNROLL];
+  const int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (g >= per_row) return;
+  const int c = (int)(VEC ? (g << 2) : g);
+  const int64_t rstride = (int64_t)gridDim.y * BIN_ROWS;
+  for (int64_t r0 = (int64_t)blockIdx.y * BIN_ROWS; r0 < rows; r0 += rstride) {
+    int lab[BIN_ROWS];
 #pragma unroll
-    for (int u = 0; u < EW_UNROLL; ++u) {
-      const int64_t i = base + u * stride;
-      r[u] = i / per_row;
-      g[u] = i - r[u] * per_row;
-      lab[u] = (i < total) ? (int)v[r[u] * ldv] : -1;
-    }
+    for (int u = 0; u < BIN_ROWS; ++u) lab[u] = (r0 + u < rows) ? (int)v[(r0 + u) * ldv] : -1;
 #pragma unroll
-    for (int u = 0; u < EW_UNROLL; ++u) {
-      const int64_t i = base + u * stride;
-      if (i >= total) continue;
-      if (VEC) {
-        const int c = (int)(g[u] << 2);
-        st4<STREAM>(out + r[u] * ldo + c,
-                    make_float4(lab[u] == c ? 1.f : 0.f, lab[u] == c + 1 ? 1.f : 0.f,
-                                lab[u] == c + 2 ? 1.f : 0.f, lab[u] == c + 3 ? 1.f : 0.f));
-      } else {
-        st1<STREAM>(out + r[u] * ldo + g[u], lab[u] == (int)g[u] ? 1.f : 0.f);
-      }
+    for (int u = 0; u < BIN_ROWS; ++u) {
+      if (r0 + u >= rows) break;
+      float* o = out + (r0 + u) * ldo + c;
+      if (VEC)
+        st4<STREAM>(o, make_float4(lab[u] == c ? 1.f : 0.f, lab[u] == c + 1 ? 1.f : 0.f,
+                                   lab[u] == c + 2 ? 1.f : 0.f, lab[u] == c + 3 ? 1.f : 0.f));
+      else
+        st1<STREAM>(o, lab[u] == c ? 1.f : 0.f);
     }
   }
 }
@@ -536,9 +535,16 @@ B200_API int b200_binarize_v(const float* v, int64_t ldv, float* out, int64_t ro
   const State& s = state();
   const bool vec = (cols % 4 == 0) && aligned16(out) && (ldo % 4 == 0);
   const bool stream = rows * cols >= STREAM_MIN_ELEMS;
-  const int64_t total = rows * (vec ? cols / 4 : cols);
-  const int threads = s.ew_threads;
-  const int grid = ew_grid(total, threads);
+  const int64_t per_row = vec ? cols / 4 : cols;
+  const int threads = per_row >= 256 ? 256 : (per_row >= 128 ? 128 : (per_row >= 64 ? 64 : 32));
+  const int64_t gx = ceil_div(per_row, threads);
+  B200_REQUIRE(gx < ((int64_t)1 << 31), "too many columns");
+  int64_t gy = ceil_div((int64_t)s.sm_count * s.ew_blocks_per_sm * 256 / threads, gx);
+  const int64_t gy_max = ceil_div(rows, BIN_ROWS);
+  if (gy > gy_max) gy = gy_max;
+  if (gy > 65535) gy = 65535;
+  if (gy < 1) gy = 1;
+  const dim3 grid((unsigned)gx, (unsigned)gy);
   if (vec) {
     if (stream) binarize_kernel<true, true><<<grid, threads, 0, s.stream>>>(v, ldv, out, rows, cols, ldo);
     else binarize_kernel<true, false><<<grid, threads, 0, s.stream>>>(v, ldv, out, rows, cols, ldo);
