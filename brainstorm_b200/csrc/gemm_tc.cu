@@ -64,6 +64,18 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       : "memory");
   return ok;
 }
+// Non-blocking phase test (try_wait may suspend the thread for a while).
+__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
 // Bounded wait.  Returns false (and raises *abort_flag) if the phase did not
 // complete within the spin limit or another role already gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
@@ -147,14 +159,59 @@ struct TcConfig {
   static constexpr int A_BYTES = TC_BM * TC_BK * 4;                      // 16 KiB
   static constexpr int B_BYTES = BN * TC_BK * 4;
   static constexpr int STAGE_BYTES = 2 * (A_BYTES + B_BYTES);            // hi + lo of both
-  static constexpr int STAGES = (BN >= 128) ? 3 : (BN >= 64) ? 4 : 5;
+  static constexpr int STAGES = (BN >= 256) ? 2 : (BN >= 128) ? 3 : (BN >= 64) ? 4 : 5;
   static constexpr int TMEM_COLS = 2 * BN;                               // two accumulator buffers
+  // Register accumulators per thread are capped at 128: a 256-wide tile is drained by
+  // two groups of four warps (the split-transform warps take columns [0, 128), the
+  // drain warps [128, 256)); narrower tiles by the drain warps alone.
+  static constexpr int DRAIN_GROUPS = (BN > 128) ? 2 : 1;
+  static constexpr int ACC = BN / DRAIN_GROUPS;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 };
 
 // The residual of the TF32 truncation, exact in fp32.
 __device__ __forceinline__ float tf32_residual(float x) {
   return x - __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
+}
+
+// acc[0..NCOLS) += the NCOLS accumulator columns at taddr of this warp's TMEM lanes
+template <int NCOLS>
+__device__ __forceinline__ void drain_add(uint32_t taddr, float (&acc)[NCOLS]) {
+#pragma unroll
+  for (int cc = 0; cc < NCOLS / 32; ++cc) {
+    float v[32];
+    tmem_ld32(taddr + (uint32_t)(cc * 32), v);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) acc[cc * 32 + j] += v[j];
+  }
+}
+
+// one output row segment: crow[col0 + j] (+)= acc[j], j < NCOLS, columns >= N masked
+template <int NCOLS>
+__device__ __forceinline__ void store_row(const float (&acc)[NCOLS], float* crow, int col0, int N,
+                                          int accumulate, bool vec_ok) {
+#pragma unroll
+  for (int cc = 0; cc < NCOLS / 32; ++cc) {
+    const int c0 = col0 + cc * 32;
+    if (vec_ok && c0 + 32 <= N) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        float4 o = make_float4(acc[cc * 32 + j], acc[cc * 32 + j + 1], acc[cc * 32 + j + 2], acc[cc * 32 + j + 3]);
+        float4* p = reinterpret_cast<float4*>(crow + c0 + j);
+        if (accumulate) {
+          const float4 old = *p;
+          o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+        }
+        *p = o;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int col = c0 + j;
+        if (col < N) crow[col] = accumulate ? crow[col] + acc[cc * 32 + j] : acc[cc * 32 + j];
+      }
+    }
+  }
 }
 
 template <int BN>
@@ -199,7 +256,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(acc_full_bar(b), 1);
-      mbar_init(acc_empty_bar(b), 128);
+      mbar_init(acc_empty_bar(b), 128 * Cfg::DRAIN_GROUPS);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -289,8 +346,16 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     }
     __syncwarp();
   } else if (warp < 6) {
-    // ---------------- split transform ----------------
+    // ---------------- split transform (and, for 256-wide tiles, half of the drain) ----------------
     const int t = threadIdx.x - 64;  // 0..127
+    const int q = warp & 3;
+    const uint32_t lane_bits = (uint32_t)(q * 32) << 16;
+    const int num_chunks = (num_kb + TC_CHUNK_KB - 1) / TC_CHUNK_KB;
+    constexpr bool kDrainsToo = Cfg::DRAIN_GROUPS == 2;
+    float acc[kDrainsToo ? Cfg::ACC : 1];
+#pragma unroll
+    for (int j = 0; j < (kDrainsToo ? Cfg::ACC : 1); ++j) acc[j] = 0.f;
+    int next_chunk = 0;
     bool ok = true;
     for (int kb = 0; kb < num_kb && ok; ++kb) {
       const int s = kb % S;
@@ -313,59 +378,63 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       }
       fence_async_smem();   // generic-proxy writes -> visible to the tensor core's async reads
       mbar_arrive(split_bar(s));
+      if (kDrainsToo) {
+        // drain every chunk that has finished, without waiting for one that has not
+        while (next_chunk < num_chunks) {
+          const int buf = next_chunk & 1;
+          const bool ready = __all_sync(0xffffffffu, mbar_test_wait(acc_full_bar(buf), (next_chunk >> 1) & 1));
+          if (!ready) break;
+          tc_fence_after();
+          drain_add<kDrainsToo ? Cfg::ACC : 32>(tmem_d + lane_bits + (uint32_t)(buf * BN), *reinterpret_cast<float(*)[kDrainsToo ? Cfg::ACC : 32]>(acc));
+          tc_fence_before();
+          mbar_arrive(acc_empty_bar(buf));
+          ++next_chunk;
+        }
+      }
+    }
+    if (kDrainsToo) {
+      for (; next_chunk < num_chunks && ok; ++next_chunk) {
+        const int buf = next_chunk & 1;
+        ok = mbar_wait(acc_full_bar(buf), (next_chunk >> 1) & 1, abort_flag);
+        __syncwarp();
+        if (!ok) break;
+        tc_fence_after();
+        drain_add<kDrainsToo ? Cfg::ACC : 32>(tmem_d + lane_bits + (uint32_t)(buf * BN), *reinterpret_cast<float(*)[kDrainsToo ? Cfg::ACC : 32]>(acc));
+        tc_fence_before();
+        mbar_arrive(acc_empty_bar(buf));
+      }
+      if (ok) {
+        const int row = m0 + q * 32 + lane;
+        const bool vec_ok = ((reinterpret_cast<uintptr_t>(c) & 15) == 0) && (ldc % 4 == 0);
+        if (row < M)
+          store_row<kDrainsToo ? Cfg::ACC : 32>(*reinterpret_cast<float(*)[kDrainsToo ? Cfg::ACC : 32]>(acc),
+                                                c + (int64_t)row * ldc, n0, N, accumulate, vec_ok);
+      }
     }
   } else {
     // ---------------- chunk drain, then epilogue ----------------
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     const uint32_t lane_bits = (uint32_t)(q * 32) << 16;
-    float acc[BN];
+    constexpr int COL0 = (Cfg::DRAIN_GROUPS == 2) ? Cfg::ACC : 0;   // first column of this group
+    float acc[Cfg::ACC];
 #pragma unroll
-    for (int j = 0; j < BN; ++j) acc[j] = 0.f;
+    for (int j = 0; j < Cfg::ACC; ++j) acc[j] = 0.f;
     const int num_chunks = (num_kb + TC_CHUNK_KB - 1) / TC_CHUNK_KB;
     bool ok = true;
     for (int chunk = 0; chunk < num_chunks && ok; ++chunk) {
       const int buf = chunk & 1;
       ok = mbar_wait(acc_full_bar(buf), (chunk >> 1) & 1, abort_flag);
+      __syncwarp();
       if (!ok) break;
       tc_fence_after();
-#pragma unroll
-      for (int cc = 0; cc < BN / 32; ++cc) {
-        float v[32];
-        tmem_ld32(tmem_d + lane_bits + (uint32_t)(buf * BN + cc * 32), v);
-#pragma unroll
-        for (int j = 0; j < 32; ++j) acc[cc * 32 + j] += v[j];
-      }
+      drain_add<Cfg::ACC>(tmem_d + lane_bits + (uint32_t)(buf * BN + COL0), acc);
       tc_fence_before();
       mbar_arrive(acc_empty_bar(buf));
     }
     if (ok) {
       const int row = m0 + q * 32 + lane;
-      float* crow = c + (int64_t)row * ldc;
       const bool vec_ok = ((reinterpret_cast<uintptr_t>(c) & 15) == 0) && (ldc % 4 == 0);
-      if (row < M) {
-#pragma unroll
-        for (int cc = 0; cc < BN / 32; ++cc) {
-          const int col0 = n0 + cc * 32;
-          if (vec_ok && col0 + 32 <= N) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              float4 o = make_float4(acc[cc * 32 + j], acc[cc * 32 + j + 1], acc[cc * 32 + j + 2], acc[cc * 32 + j + 3]);
-              float4* p = reinterpret_cast<float4*>(crow + col0 + j);
-              if (accumulate) {
-                const float4 old = *p;
-                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-              }
-              *p = o;
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int col = col0 + j;
-              if (col < N) crow[col] = accumulate ? crow[col] + acc[cc * 32 + j] : acc[cc * 32 + j];
-            }
-          }
-        }
-      }
+      if (row < M) store_row<Cfg::ACC>(acc, c + (int64_t)row * ldc, n0 + COL0, N, accumulate, vec_ok);
     }
   }
   tc_fence_before();
@@ -478,6 +547,7 @@ static int tc_setup() {
   B200_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcConfig<32>::SMEM_BYTES));
   B200_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcConfig<64>::SMEM_BYTES));
   B200_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcConfig<128>::SMEM_BYTES));
+  B200_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcConfig<256>::SMEM_BYTES));
   h.encode = (EncodeTiledFn)fn;
   return B200_OK;
 }
@@ -574,10 +644,12 @@ static int gemm_tc_impl(int transa, int transb, int64_t M, int64_t N, int64_t K,
   a = sa.ptr; lda = sa.ld;
   b = sb.ptr; ldb = sb.ld;
   // Tile width.  One tcgen05.mma costs about the same time for any N <= 128 (it is
-  // bound by streaming the 128-row A operand), so the tile is as wide as N allows.
+  // bound by streaming the 128-row A operand) and under twice that for N = 256, so
+  // the tile is as wide as N allows; 256 only while its tiles still fill the GPU.
   const int64_t tiles_m = ceil_div(M, TC_BM);
   int bn = N <= 32 ? 32 : (N <= 64 ? 64 : 128);
-  if (s.gemm_bn == 32 || s.gemm_bn == 64 || s.gemm_bn == 128) bn = s.gemm_bn;
+  if (N >= 256 && 2 * tiles_m * ceil_div(N, 256) >= s.sm_count) bn = 256;
+  if (s.gemm_bn == 32 || s.gemm_bn == 64 || s.gemm_bn == 128 || s.gemm_bn == 256) bn = s.gemm_bn;
   const int64_t tiles = tiles_m * ceil_div(N, bn);
   // Split-K when the tiles alone cannot fill the GPU: every CTA then walks a short
   // K range (a multiple of the TMEM chunk) and writes a partial tile; a second
@@ -620,6 +692,7 @@ static int gemm_tc_impl(int transa, int transb, int64_t M, int64_t N, int64_t K,
   switch (bn) {
     case 32: gemm_tf32x3_kernel<32><<<grid, TC_THREADS, TcConfig<32>::SMEM_BYTES, s.stream>>>(ma, mb, dst, m, n, k, dst_ld, acc_flag, amn, bmn, flag, kb_per_split, split_stride); break;
     case 64: gemm_tf32x3_kernel<64><<<grid, TC_THREADS, TcConfig<64>::SMEM_BYTES, s.stream>>>(ma, mb, dst, m, n, k, dst_ld, acc_flag, amn, bmn, flag, kb_per_split, split_stride); break;
+    case 256: gemm_tf32x3_kernel<256><<<grid, TC_THREADS, TcConfig<256>::SMEM_BYTES, s.stream>>>(ma, mb, dst, m, n, k, dst_ld, acc_flag, amn, bmn, flag, kb_per_split, split_stride); break;
     default: gemm_tf32x3_kernel<128><<<grid, TC_THREADS, TcConfig<128>::SMEM_BYTES, s.stream>>>(ma, mb, dst, m, n, k, dst_ld, acc_flag, amn, bmn, flag, kb_per_split, split_stride); break;
   }
   B200_LAUNCH_CHECK();
