@@ -53,12 +53,38 @@ struct State {
   int ew_blocks_per_sm = 32;
   int ew_threads = 1024;
   int gemm_path = 0;  // 0 = auto, 1 = force SIMT, 2 = force tensor-core
-  int gemm_bn = 0;    // 0 = auto, else forced tile width (32/64/128)
+  int gemm_bn = 0;    // 0 = auto, else forced tile width (32/64/128/256)
+  int use_pdl = 1;    // programmatic dependent launch inside the LSTM time loops
+  bool pdl_now = false;  // set while a time loop is issuing its kernels
 };
 State& state();
 int require_ready();
 
 static inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// Programmatic dependent launch: a kernel calls pdl_launch_dependents() to let the
+// next kernel of the stream begin its prologue early, and pdl_wait() before it
+// touches anything the previous kernel wrote or still reads.  Both are no-ops for
+// kernels launched the ordinary way.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Launch with the "programmatic stream serialization" attribute when `pdl` is set.
+template <class... KArgs, class... Args>
+static inline cudaError_t launch_maybe_pdl(bool pdl, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                           cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 // ---- device helpers -------------------------------------------------------

@@ -261,11 +261,15 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  pdl_launch_dependents();
   if (warp == 1) tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_d = *tmem_slot;
+  // everything above touched only this CTA's shared and tensor memory; operands and
+  // the output may still be in use by the previous kernel of the stream
+  pdl_wait();
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -690,10 +694,10 @@ static int gemm_tc_impl(int transa, int transb, int64_t M, int64_t N, int64_t K,
   const int m = (int)M, n = (int)N, k = (int)K;
   const int amn = transa ? 1 : 0, bmn = transb ? 0 : 1;
   switch (bn) {
-    case 32: gemm_tf32x3_kernel<32><<<grid, TC_THREADS, TcConfig<32>::SMEM_BYTES, s.stream>>>(ma, mb, dst, m, n, k, dst_ld, acc_flag, amn, bmn, flag, kb_per_split, split_stride); break;
-    case 64: gemm_tf32x3_kernel<64><<<grid, TC_THREADS, TcConfig<64>::SMEM_BYTES, s.stream>>>(ma, mb, dst, m, n, k, dst_ld, acc_flag, amn, bmn, flag, kb_per_split, split_stride); break;
-    case 256: gemm_tf32x3_kernel<256><<<grid, TC_THREADS, TcConfig<256>::SMEM_BYTES, s.stream>>>(ma, mb, dst, m, n, k, dst_ld, acc_flag, amn, bmn, flag, kb_per_split, split_stride); break;
-    default: gemm_tf32x3_kernel<128><<<grid, TC_THREADS, TcConfig<128>::SMEM_BYTES, s.stream>>>(ma, mb, dst, m, n, k, dst_ld, acc_flag, amn, bmn, flag, kb_per_split, split_stride); break;
+    case 32: B200_CUDA(launch_maybe_pdl(s.pdl_now, gemm_tf32x3_kernel<32>, grid, dim3(TC_THREADS), (size_t)TcConfig<32>::SMEM_BYTES, s.stream, ma, mb, dst, m, n, k, dst_ld, acc_flag, amn, bmn, flag, kb_per_split, split_stride)); break;
+    case 64: B200_CUDA(launch_maybe_pdl(s.pdl_now, gemm_tf32x3_kernel<64>, grid, dim3(TC_THREADS), (size_t)TcConfig<64>::SMEM_BYTES, s.stream, ma, mb, dst, m, n, k, dst_ld, acc_flag, amn, bmn, flag, kb_per_split, split_stride)); break;
+    case 256: B200_CUDA(launch_maybe_pdl(s.pdl_now, gemm_tf32x3_kernel<256>, grid, dim3(TC_THREADS), (size_t)TcConfig<256>::SMEM_BYTES, s.stream, ma, mb, dst, m, n, k, dst_ld, acc_flag, amn, bmn, flag, kb_per_split, split_stride)); break;
+    default: B200_CUDA(launch_maybe_pdl(s.pdl_now, gemm_tf32x3_kernel<128>, grid, dim3(TC_THREADS), (size_t)TcConfig<128>::SMEM_BYTES, s.stream, ma, mb, dst, m, n, k, dst_ld, acc_flag, amn, bmn, flag, kb_per_split, split_stride)); break;
   }
   B200_LAUNCH_CHECK();
   if (partials_out) {

@@ -21,6 +21,12 @@ int gemm_tc_partials(int transa, int transb, int64_t M, int64_t N, int64_t K, co
                      const float* b, int64_t ldb, float* c, int64_t ldc, const float** ptr, int* splits,
                      int64_t* split_stride, int64_t* ld);
 
+// Marks the kernels issued while it is alive as a programmatic-dependent-launch chain.
+struct PdlScope {
+  explicit PdlScope(bool on) { state().pdl_now = on; }
+  ~PdlScope() { state().pdl_now = false; }
+};
+
 enum { ACT_SIGMOID = 0, ACT_TANH = 1, ACT_REL = 2, ACT_EL = 3, ACT_LINEAR = 4 };
 
 __device__ __forceinline__ float sigmoid_dev(float x) {
@@ -68,6 +74,8 @@ struct LstmFwdStep {
 };
 
 __global__ void __launch_bounds__(256) lstm_gate_fwd_kernel(LstmFwdStep p) {
+  pdl_launch_dependents();
+  pdl_wait();   // the recurrent GEMM of this step must have finished
   const int64_t n = (int64_t)p.B * p.H;
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
@@ -115,6 +123,8 @@ struct LstmBwdStep {
 };
 
 __global__ void __launch_bounds__(256) lstm_gate_bwd_kernel(LstmBwdStep p) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t n = (int64_t)p.B * p.H;
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
@@ -172,6 +182,7 @@ B200_API int b200_lstm_forward(const float* xproj, const float* r_stack, const f
   const State& s = state();
   const int64_t bh = (int64_t)B * H;
   const unsigned grid = (unsigned)ceil_div(bh, 256);
+  PdlScope pdl_scope(s.use_pdl != 0);
   for (int t = 0; t < T; ++t) {
     const int tp = (t + T) % (T + 1);  // t - 1, wrapping to the context slot
     LstmFwdStep p;
@@ -185,7 +196,7 @@ B200_API int b200_lstm_forward(const float* xproj, const float* r_stack, const f
     p.fa = fa + t * bh; p.fb = fb + t * bh; p.oa = oa + t * bh; p.ob = ob + t * bh;
     p.ca = ca + t * bh; p.cb = cb + t * bh; p.y = y + t * bh; p.y_work = y_work + t * bh;
     p.B = B; p.H = H; p.act = act;
-    lstm_gate_fwd_kernel<<<grid, 256, 0, s.stream>>>(p);
+    B200_CUDA(launch_maybe_pdl(s.pdl_now, lstm_gate_fwd_kernel, dim3(grid), dim3(256), 0, s.stream, p));
     B200_LAUNCH_CHECK();
   }
   return B200_OK;
@@ -206,6 +217,7 @@ B200_API int b200_lstm_backward(const float* deltas, const float* r_stack, const
   const State& s = state();
   const int64_t bh = (int64_t)B * H;
   const unsigned grid = (unsigned)ceil_div(bh, 256);
+  PdlScope pdl_scope(s.use_pdl != 0);
   for (int t = T - 1; t >= 0; --t) {
     const int tp = (t + T) % (T + 1), tn = t + 1;
     LstmBwdStep p;
@@ -224,7 +236,7 @@ B200_API int b200_lstm_backward(const float* deltas, const float* r_stack, const
     p.dca = dca + t * bh; p.dcb = dcb + t * bh;
     p.dg_work = dg_work + (int64_t)t * 4 * bh;
     p.B = B; p.H = H; p.act = act;
-    lstm_gate_bwd_kernel<<<grid, 256, 0, s.stream>>>(p);
+    B200_CUDA(launch_maybe_pdl(s.pdl_now, lstm_gate_bwd_kernel, dim3(grid), dim3(256), 0, s.stream, p));
     B200_LAUNCH_CHECK();
   }
   return B200_OK;

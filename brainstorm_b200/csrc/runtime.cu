@@ -94,6 +94,7 @@ B200_API int b200_set_tuning(int key, int value) {
     case 1: B200_REQUIRE(value >= 64 && value <= 1024 && value % 32 == 0, "threads per block out of range"); s.ew_threads = value; break;
     case 2: B200_REQUIRE(value >= 0 && value <= 2, "gemm path must be 0, 1 or 2"); s.gemm_path = value; break;
     case 3: s.gemm_bn = value; break;
+    case 5: s.use_pdl = value ? 1 : 0; break;
     default: return set_error(B200_ERR_ARG, "unknown tuning key %d", key);
   }
   return B200_OK;
