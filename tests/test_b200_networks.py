@@ -136,3 +136,19 @@ def test_handler_is_describable_and_weight_modifier_runs():
         net.set_weight_modifiers({'FC': {'W': bs.value_modifiers.ConstrainL2Norm(0.5)}})
         net.apply_weight_modifiers()
     _close(net_gpu.get('parameters'), net_cpu.get('parameters'), 1e-5, 'constrained parameters')
+
+
+def test_reference_debug_handler_wraps_b200_handler():
+    """The reference's DebugHandler (shape / finite checks around every op,
+    brainstorm/handlers/debug_handler.py:61) on top of B200Handler: the array
+    contract it relies on (shape, size, reshape, indexing) must hold."""
+    from brainstorm.handlers.debug_handler import DebugHandler
+    from brainstorm_b200 import B200Handler, workloads
+    from brainstorm_b200.workloads import train_steps
+    net, data, stepper = workloads.lstm(time=4, batch=3, vocab=6, hidden=5)
+    net.set_handler(DebugHandler(B200Handler(seed=1, rng_mode='host')))
+    losses = train_steps(net, data, stepper(), 2)
+    assert np.isfinite(losses).all() and losses[1] < losses[0]
+    net2, data2, stepper2 = workloads.highway_bn(batch=12, width=8, classes=3, blocks=1)
+    net2.set_handler(DebugHandler(B200Handler(seed=1, rng_mode='host')))
+    assert np.isfinite(train_steps(net2, data2, stepper2(), 2)).all()
