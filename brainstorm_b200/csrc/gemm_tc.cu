@@ -262,6 +262,10 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   pdl_launch_dependents();
+  if (warp == 0 && lane == 0) {   // fetch the two TMA descriptors while the prologue runs
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+  }
   if (warp == 1) tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS);
   tc_fence_before();
   __syncthreads();

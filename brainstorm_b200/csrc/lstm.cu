@@ -80,27 +80,46 @@ __global__ void __launch_bounds__(256) lstm_gate_fwd_kernel(LstmFwdStep p) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const int b = (int)(i / p.H), h = (int)(i - (int64_t)b * p.H);
-  float r[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int s = 0; s < p.splits; ++s) {
-    const float* q = p.rpart + (int64_t)s * p.split_stride + (int64_t)b * p.rld + h;
-#pragma unroll
-    for (int g = 0; g < 4; ++g) r[g] = (s == 0) ? q[g * p.H] : __fadd_rn(r[g], q[g * p.H]);
-  }
+  // issue every independent load before the first use
   const float* xp = p.xproj + (int64_t)b * 4 * p.H + h;
+  const float x0 = xp[0], x1 = xp[p.H], x2 = xp[2 * p.H], x3 = xp[3 * p.H];
   const float cprev = p.ca_prev[i];
+  const float bz = p.bias[h], bi = p.bias[p.H + h], bf = p.bias[2 * p.H + h], bo = p.bias[3 * p.H + h];
+  const float wpi = p.peep[h], wpf = p.peep[p.H + h], wpo = p.peep[2 * p.H + h];
+  float r[4] = {0.f, 0.f, 0.f, 0.f};
+  const float* q0 = p.rpart + (int64_t)b * p.rld + h;
+  int s = 0;
+  for (; s + 4 <= p.splits; s += 4) {   // four splits in flight (the usual count is 4)
+    float v[4][4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int g = 0; g < 4; ++g) v[u][g] = q0[(int64_t)(s + u) * p.split_stride + g * p.H];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int g = 0; g < 4; ++g) r[g] = (s + u == 0) ? v[u][g] : __fadd_rn(r[g], v[u][g]);
+  }
+  for (; s < p.splits; ++s) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const float v = q0[(int64_t)s * p.split_stride + g * p.H];
+      r[g] = (s == 0) ? v : __fadd_rn(r[g], v);
+    }
+  }
   // block input (lstm_layer.py:117-119)
-  const float za = __fadd_rn(__fadd_rn(xp[0], r[0]), p.bias[h]);
+  const float za = __fadd_rn(__fadd_rn(x0, r[0]), bz);
   const float zb = act_fwd(p.act, za);
   // input gate (:122-125)
-  const float ia = __fadd_rn(madd(__fadd_rn(xp[p.H], r[1]), cprev, p.peep[h]), p.bias[p.H + h]);
+  const float ia = __fadd_rn(madd(__fadd_rn(x1, r[1]), cprev, wpi), bi);
   const float ib = sigmoid_dev(ia);
   // forget gate (:128-131)
-  const float fa = __fadd_rn(madd(__fadd_rn(xp[2 * p.H], r[2]), cprev, p.peep[p.H + h]), p.bias[2 * p.H + h]);
+  const float fa = __fadd_rn(madd(__fadd_rn(x2, r[2]), cprev, wpf), bf);
   const float fb = sigmoid_dev(fa);
   // cell (:134-135)
   const float ca = madd(__fmul_rn(ib, zb), fb, cprev);
   // output gate (:138-141)
-  const float oa = __fadd_rn(madd(__fadd_rn(xp[3 * p.H], r[3]), ca, p.peep[2 * p.H + h]), p.bias[3 * p.H + h]);
+  const float oa = __fadd_rn(madd(__fadd_rn(x3, r[3]), ca, wpo), bo);
   const float ob = sigmoid_dev(oa);
   // block output (:144-145)
   const float cb = act_fwd(p.act, ca);
@@ -129,31 +148,42 @@ __global__ void __launch_bounds__(256) lstm_gate_bwd_kernel(LstmBwdStep p) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const int b = (int)(i / p.H), h = (int)(i - (int64_t)b * p.H);
+  // issue every independent load before the first use
+  const float d0 = p.deltas[i];
+  const float dia_n = p.dia_n[i], dfa_n = p.dfa_n[i], dca_n = p.dca_n[i], fb_n = p.fb_n[i];
+  const float ob = p.ob[i], cb = p.cb[i], fb = p.fb[i], zb = p.zb[i], ib = p.ib[i], ca_prev = p.ca_prev[i];
   // dy = output deltas + recurrent deltas (lstm_layer.py:173-177)
-  float dy = p.deltas[i];
+  float dy = d0;
   if (p.rpart) {
+    const float* q0 = p.rpart + (int64_t)b * p.rld + h;
     float r = 0.f;
-    for (int s = 0; s < p.splits; ++s) {
-      const float v = p.rpart[(int64_t)s * p.split_stride + (int64_t)b * p.rld + h];
+    int s = 0;
+    for (; s + 8 <= p.splits; s += 8) {   // eight partials in flight
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = q0[(int64_t)(s + u) * p.split_stride];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) r = (s + u == 0) ? v[u] : __fadd_rn(r, v[u]);
+    }
+    for (; s < p.splits; ++s) {
+      const float v = q0[(int64_t)s * p.split_stride];
       r = (s == 0) ? v : __fadd_rn(r, v);
     }
     dy = __fadd_rn(dy, r);
   }
   const float pi = p.peep[h], pf = p.peep[p.H + h], po = p.peep[2 * p.H + h];
   float dca = 0.0f;                                   // :168 (dCa starts at zero)
-  dca = madd(dca, p.dia_n[i], pi);                    // :180
-  dca = madd(dca, p.dfa_n[i], pf);                    // :181
-  const float ob = p.ob[i], cb = p.cb[i];
+  dca = madd(dca, dia_n, pi);                         // :180
+  dca = madd(dca, dfa_n, pf);                         // :181
   const float dob = __fmul_rn(dy, cb);                // :184
   const float doa = sigmoid_bwd(ob, dob);             // :185
   dca = madd(dca, doa, po);                           // :187
   float dcb = __fmul_rn(dy, ob);                      // :190
   dcb = act_bwd(p.act, cb, dcb);                      // :191
   dca = __fadd_rn(dca, dcb);                          // :192
-  dca = madd(dca, p.dca_n[i], p.fb_n[i]);             // :193
-  const float dfb = __fmul_rn(dca, p.ca_prev[i]);     // :196
-  const float dfa = sigmoid_bwd(p.fb[i], dfb);        // :197
-  const float zb = p.zb[i], ib = p.ib[i];
+  dca = madd(dca, dca_n, fb_n);                       // :193
+  const float dfb = __fmul_rn(dca, ca_prev);          // :196
+  const float dfa = sigmoid_bwd(fb, dfb);             // :197
   const float dib = __fmul_rn(dca, zb);               // :200
   const float dia = sigmoid_bwd(ib, dib);             // :201
   const float dzb = __fmul_rn(dca, ib);               // :204
