@@ -131,6 +131,22 @@ class B200Array(object):
         return B200Array(self.base, self.ptr, shape, strides)
 
     def __getitem__(self, key):
+        # fast path: one integer into a contiguous array (time-step indexing in the
+        # recurrent layers: y[t - 1], Za[t], ...)
+        if self._contig and type(key) is int and self.shape:
+            n = self.shape[0]
+            if key < 0:
+                key += n
+            if not 0 <= key < n:
+                raise IndexError('index out of bounds for axis 0 with size %d' % n)
+            sub = B200Array.__new__(B200Array)
+            sub.base = self.base
+            sub.shape = self.shape[1:]
+            sub.strides = self.strides[1:]
+            sub.size = self.size // n if n else 0
+            sub.ptr = self.ptr + key * sub.size * _ITEM
+            sub._contig = True
+            return sub
         if not isinstance(key, tuple):
             key = (key,)
         if any(k is Ellipsis for k in key):

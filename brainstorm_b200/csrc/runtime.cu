@@ -178,6 +178,35 @@ B200_API int b200_memcpy2d_d2h(void* dst, uint64_t dst_pitch, uint64_t src, uint
   return gemm_tc_check_flag();
 }
 
+// ---- uploads that overlap with compute ---------------------------------------------
+// A second stream carries host->device copies so that the next batch can be uploaded
+// while kernels of the current one run.  b200_upload_async orders the copy after
+// `after_event` (an event of b200_event_record, 0 for none: the caller names the last
+// kernels that read the destination); b200_upload_join makes everything queued on the
+// compute stream afterwards wait for the uploads issued so far.
+static cudaStream_t g_copy_stream = nullptr;
+static cudaEvent_t g_copy_done = nullptr;
+
+B200_API int b200_upload_async(uint64_t dst, const void* src, uint64_t bytes, uint64_t after_event) {
+  if (int rc = require_ready()) return rc;
+  if (!g_copy_stream) {
+    B200_CUDA(cudaStreamCreateWithFlags(&g_copy_stream, cudaStreamNonBlocking));
+    B200_CUDA(cudaEventCreateWithFlags(&g_copy_done, cudaEventDisableTiming));
+  }
+  if (after_event) B200_CUDA(cudaStreamWaitEvent(g_copy_stream, (cudaEvent_t)(uintptr_t)after_event, 0));
+  if (bytes)
+    B200_CUDA(cudaMemcpyAsync((void*)(uintptr_t)dst, src, (size_t)bytes, cudaMemcpyHostToDevice, g_copy_stream));
+  return B200_OK;
+}
+
+B200_API int b200_upload_join(void) {
+  if (int rc = require_ready()) return rc;
+  if (!g_copy_stream) return B200_OK;
+  B200_CUDA(cudaEventRecord(g_copy_done, g_copy_stream));
+  B200_CUDA(cudaStreamWaitEvent(state().stream, g_copy_done, 0));
+  return B200_OK;
+}
+
 B200_API int b200_sync(void) {
   if (int rc = require_ready()) return rc;
   B200_CUDA(cudaStreamSynchronize(state().stream));

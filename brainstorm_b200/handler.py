@@ -174,6 +174,29 @@ class B200Handler(Handler):
         # Pageable sources are staged by the runtime before the call returns;
         # page-locked ones (pinned_empty) must stay untouched until synchronize().
 
+    def upload_async(self, mem, arr, after_event=0):
+        """Start copying the page-locked float32 array ``arr`` (see pinned_empty)
+        into the contiguous device array ``mem`` on the upload stream, after the
+        event ``after_event`` (record_event) if given.  Kernels queued after
+        ``upload_join()`` see the data."""
+        arr = np.asarray(arr)
+        if arr.dtype != _f32 or not arr.flags.c_contiguous or arr.size != mem.size or not mem._contig:
+            raise ValueError('upload_async needs a contiguous float32 source of the same size '
+                             'and a contiguous destination')
+        check(lib.b200_upload_async(mem.ptr, arr.ctypes.data, arr.nbytes, after_event))
+
+    def upload_join(self):
+        check(lib.b200_upload_join())
+
+    def record_event(self, event=None):
+        """Record (and create if needed) an event on the compute stream."""
+        if event is None:
+            e = ctypes.c_uint64()
+            check(lib.b200_event_create(_byref(e)))
+            event = e.value
+        check(lib.b200_event_record(event))
+        return event
+
     def get_numpy_copy(self, mem):
         assert type(mem) == self.array_type
         out = np.empty(mem.shape, dtype=_f32)

@@ -59,6 +59,15 @@ int b200_memcpy2d_h2d(uint64_t dst, uint64_t dst_pitch, const void* src, uint64_
 int b200_memcpy2d_d2h(void* dst, uint64_t dst_pitch, uint64_t src, uint64_t src_pitch,
                       uint64_t row_bytes, uint64_t rows);                 /* synchronises */
 
+/* Uploads on a second stream, so that the next batch's host->device copy overlaps the
+ * current batch's kernels (the input side of Network.provide_external_data,
+ * brainstorm/structure/network.py:399-403).  The copy starts after `after_event` (an
+ * event recorded with b200_event_record; 0 = at once); b200_upload_join makes work
+ * queued on the compute stream afterwards wait for all uploads issued so far.  The
+ * host source must be page-locked and stay untouched until then. */
+int b200_upload_async(uint64_t dst, const void* src, uint64_t bytes, uint64_t after_event);
+int b200_upload_join(void);
+
 /* ---- CUDA-event timing on the library stream (benchmark support) --------- */
 int b200_event_create(uint64_t* ev);
 int b200_event_record(uint64_t ev);

@@ -241,3 +241,26 @@ def test_gemm_views_of_one_flat_buffer(H):
         H.dot_mm(da, dw, out, transb=True)
         O.dot_mm(a, w, want, transb=True)
         parity.assert_reduction_close(H.get_numpy_copy(out), want, np.abs(a) @ np.abs(w.T), 'dot_mm', 'offset %d' % off)
+
+
+def test_overlapped_upload_orders_with_compute(H):
+    """upload_async / upload_join: a batch uploaded on the second stream while
+    kernels run is visible to the kernels queued after the join, and an upload into
+    a buffer waits for the event of the kernels that still read it."""
+    n = 1 << 22
+    src0, src1 = H.pinned_empty((n,)), H.pinned_empty((n,))
+    src0[:] = np.arange(n, dtype=np.float32)
+    src1[:] = -np.arange(n, dtype=np.float32)
+    buf, out = H.allocate((n,)), H.allocate((n,))
+    H.upload_async(buf, src0)
+    H.upload_join()
+    H.mult_st(2.0, buf, out)                 # reads buf
+    ev = H.record_event()
+    H.upload_async(buf, src1, ev)            # may not overwrite buf before the kernel above is done
+    first = H.get_numpy_copy(out)
+    H.upload_join()
+    H.mult_st(2.0, buf, out)
+    second = H.get_numpy_copy(out)
+    assert np.array_equal(first, 2 * src0) and np.array_equal(second, 2 * src1)
+    with pytest.raises(ValueError):
+        H.upload_async(buf, np.zeros(n - 1, np.float32))
