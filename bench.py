@@ -294,7 +294,7 @@ def lstm_training(H, world, rank, steps, barrier, lib, check):
             'parallelism': 'dp%d, gradient all-reduce (avg) of %d parameters' % (world, net.buffer.parameters.size)}
 
 
-def other_training_configs(H, rank, lib):
+def other_training_configs(H, rank, lib, only=None):
     """Single-GPU step times of the two other training workloads (extra keys of
     the bench line): the MNIST-style MLP (batch 100, momentum SGD) and the Highway +
     BatchNorm stack (batch 8192, width 4096, 10 blocks)."""
@@ -305,6 +305,8 @@ def other_training_configs(H, rank, lib):
     from brainstorm_b200 import workloads
     out = {}
     for name, build, steps in (('mlp', workloads.mlp, 50), ('highway_bn', workloads.highway_bn, 3)):
+        if only and name != only:
+            continue
         net, data, stepper = build()
         net.set_handler(H)
         st = stepper()
@@ -367,6 +369,16 @@ def run_b200(args):
 
     if args.only == 'gemm':
         return run_gemm(args, H, lib, check, new_event, elapsed)
+    if args.only in ('mlp', 'highway_bn'):
+        ref = os.path.join(ROOT, 'baseline', '_ref')
+        if os.path.isdir(os.path.join(ref, 'brainstorm')) and ref not in sys.path:
+            sys.path.insert(0, ref)
+        res = other_training_configs(H, rank, lib, only=args.only)
+        if rank == 0:
+            print(json.dumps({'metric': '%s_train_samples_per_s' % args.only,
+                              'value': res.get(args.only, {}).get('samples_per_s'), 'unit': 'samples/s',
+                              'n_gpus': world, 'detail': res}))
+        return
     if args.only == 'lstm':
         lstm = lstm_training(H, world, rank, max(1, args.steps), barrier, lib, check)
         if rank == 0:
@@ -585,7 +597,7 @@ def main():
     ap.add_argument('--steps', type=int, default=30)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
-    ap.add_argument('--only', default='all', choices=['all', 'suite', 'gemm', 'lstm'],
+    ap.add_argument('--only', default='all', choices=['all', 'suite', 'gemm', 'lstm', 'mlp', 'highway_bn'],
                     help='suite: device-resident op suite only; gemm: one dot_mm shape (for profiling)')
     ap.add_argument('--rows', type=int, default=ROWS, help='rows of the op-suite operands (default 65536)')
     ap.add_argument('--gemm', default='8192,4096,4096', help='M,N,K for --only gemm')

@@ -294,18 +294,34 @@ mv_vec(const float* m, const float* v, float* out, int64_t rows, int cols4, int6
   }
 }
 
+// Scalar form of the same walk for operands that are not 16-byte aligned (views at
+// odd element offsets of a flat buffer): a thread owns ONE column, consecutive
+// threads consecutive columns (coalesced), four rows in flight, no index division.
 template <class F, bool COL>
 __global__ void __launch_bounds__(1024)
 mv_scalar(const float* m, const float* v, float* out, int64_t rows, int64_t cols, int64_t ldm,
           int64_t ldo, Params p) {
-  const int64_t n = rows * cols;
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-    const int64_t r = i / cols, c = i - r * cols;
-    const float a = m[r * ldm + c];
-    const float b = v[COL ? r : c];
-    const float cc = (F::NIN > 2) ? out[r * ldo + c] : 0.f;
-    out[r * ldo + c] = F::apply(a, b, cc, p);
+  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  const float vr = COL ? 0.f : v[c];
+  const int64_t rstride = (int64_t)gridDim.y * blockDim.y;
+  for (int64_t r0 = (int64_t)blockIdx.y * blockDim.y + threadIdx.y; r0 < rows; r0 += rstride * EW_UNROLL) {
+    float a[EW_UNROLL], cc[EW_UNROLL], vc[EW_UNROLL];
+#pragma unroll
+    for (int u = 0; u < EW_UNROLL; ++u) {
+      const int64_t r = r0 + u * rstride;
+      a[u] = 0.f; cc[u] = 0.f; vc[u] = 0.f;
+      if (r < rows) {
+        a[u] = m[r * ldm + c];
+        if (F::NIN > 2) cc[u] = out[r * ldo + c];
+        if (COL) vc[u] = v[r];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < EW_UNROLL; ++u) {
+      const int64_t r = r0 + u * rstride;
+      if (r < rows) out[r * ldo + c] = F::apply(a[u], COL ? vc[u] : vr, cc[u], p);
+    }
   }
 }
 
@@ -345,8 +361,18 @@ static int launch_mv(const float* m, const float* v, float* out, int64_t rows, i
       else mv_vec<F, false, false><<<grid, threads, 0, s.stream>>>(m, v, out, rows, cols4, ldm, ldo, p);
     }
   } else {
-    const int threads = s.ew_threads;
-    const int grid = ew_grid(rows * cols * EW_UNROLL, threads);
+    const int tx = cols >= 256 ? 256 : (cols >= 128 ? 128 : (cols >= 64 ? 64 : 32));
+    int ty = s.ew_threads / tx;
+    if (ty < 1) ty = 1;
+    while (ty > 1 && (int64_t)ty * EW_UNROLL > rows) ty >>= 1;
+    const int64_t gx = ceil_div(cols, tx);
+    B200_REQUIRE(gx < ((int64_t)1 << 31), "too many columns");
+    int64_t gy = ceil_div((int64_t)s.sm_count * s.ew_blocks_per_sm, gx);
+    const int64_t gy_max = ceil_div(rows, (int64_t)ty * EW_UNROLL);
+    if (gy > gy_max) gy = gy_max;
+    if (gy > 65535) gy = 65535;
+    if (gy < 1) gy = 1;
+    const dim3 grid((unsigned)gx, (unsigned)gy), threads(tx, ty);
     if (v_is_col) mv_scalar<F, true><<<grid, threads, 0, s.stream>>>(m, v, out, rows, cols, ldm, ldo, p);
     else mv_scalar<F, false><<<grid, threads, 0, s.stream>>>(m, v, out, rows, cols, ldm, ldo, p);
   }
