@@ -173,12 +173,31 @@ class ClockSampler(object):
 
 
 # ------------------------------------------------------------------ CPU legs
+def cpu_handler():
+    """The CPU side of the comparison: the reference's own NumpyHandler when an
+    install of the reference is present (kind 'reference'), else the oracle port of it
+    (kind 'port')."""
+    ref = os.path.join(ROOT, 'baseline', '_ref')
+    if os.path.isdir(os.path.join(ref, 'brainstorm')) and ref not in sys.path:
+        sys.path.insert(0, ref)
+    try:
+        import warnings
+        with warnings.catch_warnings():
+            warnings.simplefilter('ignore')
+            from brainstorm.handlers import NumpyHandler
+        return NumpyHandler(np.float32), 'reference'
+    except Exception:
+        from oracle.numpy_oracle import OracleHandler
+        return OracleHandler(np.float32), 'port'
+
+
 def cpu_suite_time(rows, cols, seed, threads, steps, warmup):
-    """Times the oracle (CPU restatement of NumpyHandler) on `rows` rows, split
-    into row chunks over `threads` host threads (numpy releases the GIL)."""
+    """Times the CPU handler (see cpu_handler) on `rows` rows, split into row chunks
+    over `threads` host threads (numpy releases the GIL).  Returns GB/s, seconds per
+    step and the kind of handler used."""
     from concurrent.futures import ThreadPoolExecutor
-    from oracle.numpy_oracle import OracleHandler, op_suite_inputs
-    O = OracleHandler(np.float32)
+    from oracle.numpy_oracle import op_suite_inputs
+    O, kind = cpu_handler()
     d = op_suite_inputs(rows, cols, seed)
     labels = d['labels'].astype(np.float32)
     y = np.zeros_like(d['a'])
@@ -212,7 +231,7 @@ def cpu_suite_time(rows, cols, seed, threads, steps, warmup):
             step(pool)
         dt = (time.perf_counter() - t0) / steps
     nbytes = sum(b for _, b in suite_bytes(rows, cols))
-    return nbytes / dt / 1e9, dt
+    return nbytes / dt / 1e9, dt, kind
 
 
 def run_reference(args):
@@ -221,7 +240,7 @@ def run_reference(args):
         return
     threads = os.cpu_count() or 1
     steps = max(1, min(args.steps, 5))
-    gbs, dt = cpu_suite_time(CPU_SAMPLE_ROWS, COLS, SEED, threads, steps, min(args.warmup, 1))
+    gbs, dt, kind = cpu_suite_time(CPU_SAMPLE_ROWS, COLS, SEED, threads, steps, min(args.warmup, 1))
     sample = '%d of %d rows per step (same %d columns, same ops), %d steps' % (
         CPU_SAMPLE_ROWS, ROWS, COLS, steps)
     line = {
@@ -231,7 +250,7 @@ def run_reference(args):
         'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic (seeded)',
         'config': {'workload': 'handler op suite, fp32 (%d, %d) operands' % (ROWS, COLS),
                    'sample_rows': CPU_SAMPLE_ROWS, 'cols': COLS, 'seed': SEED},
-        'cpu_baseline': {'value': round(gbs, 3), 'unit': UNIT, 'cores': threads, 'kind': 'port',
+        'cpu_baseline': {'value': round(gbs, 3), 'unit': UNIT, 'cores': threads, 'kind': kind,
                          'sample': sample},
         'e2e': {'value': round(gbs, 3), 'unit': UNIT, 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
         'gpu_launches': 0,
@@ -533,8 +552,8 @@ def run_b200(args):
         cpu = None
         if world == 1 or True:
             threads = os.cpu_count() or 1
-            cgbs, cdt = cpu_suite_time(CPU_SAMPLE_ROWS, COLS, SEED, threads, 2, 1)
-            cpu = {'value': round(cgbs, 3), 'unit': UNIT, 'cores': threads, 'kind': 'port',
+            cgbs, cdt, ckind = cpu_suite_time(CPU_SAMPLE_ROWS, COLS, SEED, threads, 2, 1)
+            cpu = {'value': round(cgbs, 3), 'unit': UNIT, 'cores': threads, 'kind': ckind,
                    'sample': '%d of %d rows per step (same %d columns, same ops), 2 steps after 1 warm-up, '
                              'row chunks over %d threads' % (CPU_SAMPLE_ROWS, ROWS, COLS, threads)}
         line = {

@@ -28,10 +28,13 @@ struct Params {
 
 __device__ __forceinline__ float sigmoid_f(float x) {
   // sign-split stable form: 1/(1+exp(-x)) for x >= 0, exp(x)/(1+exp(x)) for x < 0
-  // One correctly rounded reciprocal instead of an IEEE division: r = 1/(1+e) is the
-  // x >= 0 result to 0.5 ulp; e*r differs from e/(1+e) by at most 1 ulp more.
+  // A refined hardware reciprocal instead of an IEEE division: r = 1/(1+e) is the
+  // x >= 0 result to under 1 ulp; e*r differs from e/(1+e) by at most 1 ulp more.
   const float e = expf(-fabsf(x));
-  const float r = __frcp_rn(1.0f + e);
+  const float d = 1.0f + e;                       // in (1, 2]: no special cases
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d));
+  r = fmaf(fmaf(-d, r, 1.0f), r, r);              // one Newton step: below 1 ulp
   return (x >= 0.0f) ? r : __fmul_rn(e, r);
 }
 __device__ __forceinline__ float sign_f(float x) {

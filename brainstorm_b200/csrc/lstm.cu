@@ -31,7 +31,10 @@ enum { ACT_SIGMOID = 0, ACT_TANH = 1, ACT_REL = 2, ACT_EL = 3, ACT_LINEAR = 4 };
 
 __device__ __forceinline__ float sigmoid_dev(float x) {
   const float e = expf(-fabsf(x));
-  const float r = __frcp_rn(1.0f + e);
+  const float d = 1.0f + e;
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d));
+  r = fmaf(fmaf(-d, r, 1.0f), r, r);
   return (x >= 0.0f) ? r : __fmul_rn(e, r);
 }
 __device__ __forceinline__ float act_fwd(int act, float x) {

@@ -152,3 +152,32 @@ def test_reference_debug_handler_wraps_b200_handler():
     net2, data2, stepper2 = workloads.highway_bn(batch=12, width=8, classes=3, blocks=1)
     net2.set_handler(DebugHandler(B200Handler(seed=1, rng_mode='host')))
     assert np.isfinite(train_steps(net2, data2, stepper2(), 2)).all()
+
+
+def test_reference_trainer_with_iterators_and_hooks():
+    """The reference's Trainer loop, Minibatches iterator, momentum stepper and
+    hooks (MonitorLoss on a validation iterator, StopOnNan -> is_fully_finite,
+    StopAfterEpoch), unchanged, on B200Handler vs NumpyHandler."""
+    import brainstorm as bs
+    from brainstorm.handlers import NumpyHandler
+    from brainstorm_b200 import B200Handler, workloads
+    rs = np.random.RandomState(4)
+    x = rs.uniform(0, 1, (1, 64, 20)).astype(np.float32)
+    t = rs.randint(0, 4, (1, 64, 1)).astype(np.int32)
+    logs = []
+    for handler in (NumpyHandler(np.float32, seed=9), B200Handler(seed=9, rng_mode='host')):
+        bs.global_rnd.set_seed(11)
+        net, _, _ = workloads.mlp(batch=16, hidden=24, n_in=20, n_out=4)
+        net.set_handler(handler)
+        trainer = bs.Trainer(bs.training.MomentumStepper(learning_rate=0.1, momentum=0.9), verbose=False)
+        trainer.add_hook(bs.hooks.MonitorLoss('valid', name='valid_loss', verbose=False))
+        trainer.add_hook(bs.hooks.StopOnNan())
+        trainer.add_hook(bs.hooks.StopAfterEpoch(3))
+        trainer.train(net, bs.data_iterators.Minibatches(16, shuffle=False, default=x, targets=t),
+                      valid=bs.data_iterators.Minibatches(32, shuffle=False, default=x, targets=t))
+        logs.append((trainer.logs['rolling_training']['total_loss'], trainer.logs['valid_loss']['total_loss'],
+                     net.get('parameters')))
+        assert trainer.current_epoch_nr == 3 and trainer.current_update_nr == 12
+    np.testing.assert_allclose(logs[1][0], logs[0][0], rtol=2e-4)
+    np.testing.assert_allclose(logs[1][1], logs[0][1], rtol=2e-4)
+    _close_l2(logs[1][2], logs[0][2], 1e-3, 'parameters after 3 epochs')
