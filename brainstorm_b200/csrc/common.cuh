@@ -11,7 +11,6 @@
 #define B200_OK 0
 #define B200_ERR_CUDA 1
 #define B200_ERR_ARG 2
-#define B200_ERR_NCCL 3
 #define B200_ERR_DEVICE_FLAG 4
 #define B200_ERR_UNSUPPORTED 5
 

@@ -515,7 +515,6 @@ struct TcHost {
   EncodeTiledFn encode = nullptr;
   int* error_flag_host = nullptr;   // mapped pinned memory
   int* error_flag_dev = nullptr;
-  bool attrs_set = false;
   float* partial = nullptr;         // split-K partial tiles (stream-ordered allocation)
   size_t partial_bytes = 0;
   std::mutex mu;

@@ -20,7 +20,7 @@ import ctypes
 import numpy as np
 
 from ._lib import lib, check, B200Error  # noqa: F401
-from .array import B200Array, Allocation
+from .array import B200Array
 from .handler_api import Handler, new_random_state
 
 _f32 = np.float32
@@ -86,7 +86,7 @@ class B200Handler(Handler):
     """
     __undescribed__ = {'context', 'dtype', 'EMPTY', 'rnd', 'device', 'seed', 'rng_mode',
                        '_scratch', '_flags', '_flag_host', '_rng_calls', '_label_check',
-                       '_pinned', '_comm', 'axis0_reduce', '_grad_range'}
+                       '_pinned', '_comm', 'axis0_reduce'}
 
     array_type = B200Array
 
@@ -95,8 +95,6 @@ class B200Handler(Handler):
         import os
         if device is None:
             device = int(os.environ.get('LOCAL_RANK', '0'))
-        n = ctypes.c_int(0)
-        check(lib.b200_device_count(_byref(n)))
         check(lib.b200_init(int(device)))
         if rng_mode not in ('device', 'host'):
             raise ValueError("rng_mode must be 'device' or 'host'")
@@ -115,7 +113,6 @@ class B200Handler(Handler):
         self._pinned = []
         self._comm = None
         self.axis0_reduce = 'local'
-        self._grad_range = None
 
     def __describe__(self):
         return {'@type': self.__class__.__name__}
@@ -212,6 +209,13 @@ class B200Handler(Handler):
         if self._label_check:
             self._raise_on_bad_labels()
         return out
+
+    def device_info(self):
+        """(device ordinal, SM count, free bytes, total bytes) of this handler's GPU."""
+        dev, sms = ctypes.c_int(), ctypes.c_int()
+        free, total = ctypes.c_uint64(), ctypes.c_uint64()
+        check(lib.b200_device_info(_byref(dev), _byref(sms), _byref(free), _byref(total)))
+        return dev.value, sms.value, free.value, total.value
 
     def synchronize(self):
         check(lib.b200_sync())

@@ -46,6 +46,43 @@ class Comm(object):
             self._stream = torch.cuda.ExternalStream(lib.b200_stream())
         return self._stream
 
+    def allreduce_async(self, arr, op='sum'):
+        """Start an in-place all-reduce and return a handle for ``wait``.  On the GPU
+        the collective is ordered after the kernels queued so far, and kernels queued
+        after this call do NOT wait for it until ``wait(handle)``."""
+        import torch
+        if self.world == 1 or arr.size == 0:
+            return None
+        if isinstance(arr, np.ndarray):
+            if not arr.flags.c_contiguous:
+                raise NotImplementedError('asynchronous all-reduce of a strided host view')
+            buf = arr.reshape(-1)
+            work = self.dist.all_reduce(torch.from_numpy(buf), op=self.dist.ReduceOp.SUM, async_op=True)
+            return (work, buf if op == 'avg' else None)
+        if not arr.is_contiguous:
+            raise NotImplementedError('all-reduce of a strided device view')
+        flat = arr.reshape((arr.size,))
+        with torch.cuda.stream(self._device_stream()):
+            t = torch.as_tensor(flat, device='cuda')
+            work = self.dist.all_reduce(
+                t, op=self.dist.ReduceOp.AVG if op == 'avg' else self.dist.ReduceOp.SUM, async_op=True)
+        return (work, None)
+
+    def wait(self, handle):
+        if handle is None:
+            return
+        work, host_avg = handle
+        if host_avg is not None:
+            work.wait()
+            host_avg /= host_avg.dtype.type(self.world)
+            return
+        import torch
+        if torch.cuda.is_available() and self._stream is not None:
+            with torch.cuda.stream(self._device_stream()):
+                work.wait()          # the library stream waits; the host does not
+        else:
+            work.wait()
+
     def allreduce(self, arr, op='sum'):
         """In-place all-reduce of a numpy array (gloo) or a device array (NCCL)."""
         import torch
@@ -109,22 +146,61 @@ def shard_batch(data, rank, world):
     return out
 
 
-def data_parallel(net, comm, axis0_reduce='local'):
+def _element_offset(view, flat):
+    """Offset of ``view`` inside ``flat`` in elements (numpy or device arrays)."""
+    if isinstance(view, np.ndarray):
+        return (view.__array_interface__['data'][0] - flat.__array_interface__['data'][0]) // flat.itemsize
+    return (view.ptr - flat.ptr) // 4
+
+
+def data_parallel(net, comm, axis0_reduce='local', overlap=True):
     """Make ``net`` (already on its handler) train data-parallel over ``comm``.
 
     Wraps ``net.backward_pass`` of this instance so that the flat gradient vector
     is averaged over the ranks before the stepper reads it (steppers.py:61-69), and
     switches the handler's axis-0 sums to ``axis0_reduce``.  The Trainer, steppers
-    and layers stay unchanged."""
+    and layers stay unchanged.
+
+    With ``overlap`` the all-reduce is issued per layer, as soon as that layer's
+    backward pass has been queued (the gradients of one layer are one contiguous
+    block of the flat vector, brainstorm/structure/layout.py:149-157), so the
+    collective of layer k runs while the layers before it are still computing.
+    Networks with gradient modifiers fall back to one all-reduce at the end, since
+    the modifiers run inside the reference's backward_pass (network.py:445)."""
     handler = net.handler
     if not hasattr(handler, 'set_comm'):
         raise TypeError('handler %r cannot complete sums across ranks' % (handler,))
     handler.set_comm(comm, axis0_reduce)
     local_backward = net.backward_pass
+    pending = []
 
     def backward_pass():
+        del pending[:]
         local_backward()
-        comm.allreduce(net.buffer.gradients, 'avg')
+        if pending:
+            for h in pending:
+                comm.wait(h)
+            del pending[:]
+        else:
+            comm.allreduce(net.buffer.gradients, 'avg')
 
     net.backward_pass = backward_pass
+
+    if overlap and hasattr(comm, 'allreduce_async') and not getattr(net, 'gradient_modifiers', None):
+        def wrap(name, layer):
+            layer_backward = layer.backward_pass
+
+            def layer_backward_then_reduce(buffers):
+                layer_backward(buffers)
+                flat = net.buffer.gradients
+                views = list(net.buffer[name].gradients)
+                lo = min(_element_offset(v, flat) for v in views)
+                hi = max(_element_offset(v, flat) + v.size for v in views)
+                pending.append(comm.allreduce_async(flat[lo:hi], 'avg'))
+
+            layer.backward_pass = layer_backward_then_reduce
+
+        for name, layer in net.layers.items():
+            if 'gradients' in net.buffer[name] and len(net.buffer[name].gradients):
+                wrap(name, layer)
     return net

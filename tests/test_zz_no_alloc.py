@@ -4,8 +4,6 @@ because they must never enter the CUDA allocator mid-run.  The entry point keeps
 its partial sums in an array built into the library; it must give exactly what
 b200_sum_t gives with caller-provided scratch, also when called twice in a row
 (the array still holds the previous call's partials)."""
-import ctypes
-
 import numpy as np
 import pytest
 
