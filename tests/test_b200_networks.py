@@ -79,8 +79,9 @@ def test_lstm_aligned_sizes_use_tensor_cores():
 @pytest.mark.parametrize('shape', [dict(time=7, batch=9, vocab=23, hidden=32),
                                    dict(time=6, batch=64, vocab=48, hidden=128),
                                    dict(time=1, batch=5, vocab=7, hidden=12),
-                                   dict(time=12, batch=128, vocab=205, hidden=200)],
-                         ids=['ragged', 'aligned', 'one-step', 'wide'])
+                                   dict(time=12, batch=128, vocab=205, hidden=200),
+                                   dict(time=4, batch=3, vocab=5, hidden=5)],
+                         ids=['ragged', 'aligned', 'one-step', 'wide', 'odd'])
 def test_fused_lstm_layer_matches_reference_layer(shape):
     """The fused layer on the GPU against the reference's own LstmLayerImpl on
     NumpyHandler: loss, every gradient, parameters after SGD steps -- and every
