@@ -276,6 +276,11 @@ def lstm_training(H, world, rank, steps, barrier, lib, check):
     from brainstorm_b200.fused_lstm import fuse_lstm_layers
     T, B = 100, 128
     net, data, stepper = workloads.lstm(time=T, batch=B, data_seed=rank)
+    pinned = {}
+    for k, v in data.items():                     # host batches live in page-locked memory
+        pinned[k] = H.pinned_empty(v.shape, np.float32)
+        pinned[k][...] = v
+    data = pinned
     net.set_handler(H)
     fuse_lstm_layers(net)
     if world > 1:
