@@ -534,13 +534,77 @@ class B200Handler(Handler):
         if dst is not mask:
             self.copy_to(dst, mask)
 
-    # --------------------------------------------- convolution / pooling: not built
-    def _not_built(self, *args, **kwargs):
-        raise NotImplementedError('convolution and pooling are not part of the B200 backend')
+    # ------------------------------------------------------- convolution / pooling
+    @staticmethod
+    def _nhwc(a, what):
+        if len(a.shape) != 4 or not a._contig:
+            raise ValueError('%s must be a contiguous (N, H, W, C) array, got %r' % (what, a.shape))
+        return a.shape
 
-    conv2d_forward_batch = conv2d_backward_batch = _not_built
-    maxpool2d_forward_batch = maxpool2d_backward_batch = _not_built
-    avgpool2d_forward_batch = avgpool2d_backward_batch = _not_built
+    def conv2d_forward_batch(self, inputs, weights, bias, outputs, padding, stride):
+        N, H, W, C = self._nhwc(inputs, 'inputs')
+        F, kh, kw, wc = self._nhwc(weights, 'weights')
+        on, oh, ow, of = self._nhwc(outputs, 'outputs')
+        if wc != C or on != N or of != F:
+            raise ValueError('conv2d_forward_batch: shapes %r, %r, %r do not agree' % (
+                inputs.shape, weights.shape, outputs.shape))
+        if N * oh * ow == 0:
+            return
+        K = kh * kw * C
+        col = B200Array.empty((N * oh * ow, K), zero=False)
+        check(lib.b200_im2col(inputs.ptr, col.ptr, N, H, W, C, kh, kw, padding, stride[0], stride[1], oh, ow))
+        out2 = outputs.reshape((N * oh * ow, F))
+        self.dot_mm(col, weights.reshape((F, K)), out2, transb=True)
+        self.add_mv(out2, bias.reshape((1, F)), out2)
+
+    def conv2d_backward_batch(self, inputs, params, padding, stride, in_deltas, out_deltas, dparams, dbias):
+        N, H, W, C = self._nhwc(inputs, 'inputs')
+        F, kh, kw, wc = self._nhwc(params, 'params')
+        on, oh, ow, of = self._nhwc(out_deltas, 'out_deltas')
+        self._nhwc(in_deltas, 'in_deltas')
+        if wc != C or on != N or of != F or in_deltas.shape != inputs.shape:
+            raise ValueError('conv2d_backward_batch: shapes do not agree')
+        K = kh * kw * C
+        if N * oh * ow == 0:
+            self.fill(dparams, 0.0)
+            self.fill(dbias, 0.0)
+            return
+        col = B200Array.empty((N * oh * ow, K), zero=False)
+        check(lib.b200_im2col(inputs.ptr, col.ptr, N, H, W, C, kh, kw, padding, stride[0], stride[1], oh, ow))
+        od = out_deltas.reshape((N * oh * ow, F))
+        # the reference overwrites the gradients (fill 0, then the sum over images)
+        self.dot_mm(od, col, dparams.reshape((F, K)), transa=True)
+        self.sum_t(od, 0, dbias.reshape((F,)) if dbias._contig else dbias)
+        self.dot_mm(od, params.reshape((F, K)), col)
+        check(lib.b200_col2im_add(col.ptr, in_deltas.ptr, N, H, W, C, kh, kw, padding, stride[0], stride[1], oh, ow))
+
+    def _pool(self, fwd, mode, inputs, window, outputs, padding, stride, argmax, in_deltas, out_deltas):
+        N, H, W, C = self._nhwc(inputs, 'inputs')
+        on, oh, ow, oc = self._nhwc(outputs, 'outputs')
+        if on != N or oc != C:
+            raise ValueError('pooling: inputs %r and outputs %r do not agree' % (inputs.shape, outputs.shape))
+        am = argmax.ptr if argmax is not None else 0
+        if fwd:
+            check(lib.b200_pool2d_forward(mode, inputs.ptr, outputs.ptr, am, N, H, W, C, window[0], window[1],
+                                          padding, stride[0], stride[1], oh, ow))
+        else:
+            self._nhwc(in_deltas, 'in_deltas')
+            self._nhwc(out_deltas, 'out_deltas')
+            check(lib.b200_pool2d_backward(mode, out_deltas.ptr, am, in_deltas.ptr, N, H, W, C, window[0],
+                                           window[1], padding, stride[0], stride[1], oh, ow))
+
+    def maxpool2d_forward_batch(self, inputs, window, outputs, padding, stride, argmax):
+        self._nhwc(argmax, 'argmax')
+        self._pool(True, 0, inputs, window, outputs, padding, stride, argmax, None, None)
+
+    def maxpool2d_backward_batch(self, inputs, window, outputs, padding, stride, argmax, in_deltas, out_deltas):
+        self._pool(False, 0, inputs, window, outputs, padding, stride, argmax, in_deltas, out_deltas)
+
+    def avgpool2d_forward_batch(self, inputs, window, outputs, padding, stride):
+        self._pool(True, 1, inputs, window, outputs, padding, stride, None, None, None)
+
+    def avgpool2d_backward_batch(self, inputs, window, outputs, padding, stride, in_deltas, out_deltas):
+        self._pool(False, 1, inputs, window, outputs, padding, stride, None, in_deltas, out_deltas)
 
     # ------------------------------------------------------------------ helpers
     def _contiguous_copy(self, a):

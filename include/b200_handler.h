@@ -194,6 +194,19 @@ int b200_lstm_backward(const float* deltas, const float* r_stack, const float* p
                        float* dza, float* dzb, float* dia, float* dib, float* dfa, float* dfb, float* doa, float* dob,
                        float* dca, float* dcb, float* dg_work, float* r_work, int T, int B, int H, int act);
 
+/* ---- convolution and pooling (NHWC): conv2d_forward_batch :411, conv2d_backward_batch :392,
+ *      maxpool2d_* :590/:572, avgpool2d_* :314/:297; numpy_handler.py:149,110,216,210,94,89 with
+ *      the loops of brainstorm/handlers/_cpuop.pyx.  Convolution is im2col over all images
+ *      + the GEMM above (col is (N*oh*ow, kh*kw*C), channel fastest); col2im ADDS the
+ *      columns back into in_deltas.  Pooling mode 0 = max (argmax holds the float index
+ *      (y*W + x)*C + c inside the image, -1 for an empty window, as _cpuop.pyx:27 does),
+ *      mode 1 = average over the non-padding pixels; the backward forms ADD into
+ *      in_deltas.  Gather-form kernels, no atomics. ----------------------------------- */
+int b200_im2col(const float* inputs, float* col, int N, int H, int W, int C, int kh, int kw, int pad, int sy, int sx, int oh, int ow);
+int b200_col2im_add(const float* col, float* in_deltas, int N, int H, int W, int C, int kh, int kw, int pad, int sy, int sx, int oh, int ow);
+int b200_pool2d_forward(int mode, const float* inputs, float* outputs, float* argmax, int N, int H, int W, int C, int kh, int kw, int pad, int sy, int sx, int oh, int ow);
+int b200_pool2d_backward(int mode, const float* out_deltas, const float* argmax, float* in_deltas, int N, int H, int W, int C, int kh, int kw, int pad, int sy, int sx, int oh, int ow);
+
 /* ---- random: generate_probability_mask :507, fill_gaussian :494;
  *      numpy_handler.py:199,193.  Device-side Philox4x32-10 streams addressed by
  *      (seed, offset); the host-RNG parity mode of the Python handler does not

@@ -389,3 +389,119 @@ def lstm_backward(O, p, x, f, deltas, d, grads, dx, activation='tanh'):
         O.mult_tt(d['dCa'][-1], d['dIa'][0], one)
         O.sum_t(one, 0, dWc)
         O.add_tt(grads['p' + g], dWc, grads['p' + g])
+
+
+# --------------------------------------------------------------------------
+# Convolution and pooling (NHWC), restated from numpy_handler.py:89-171,210-219 and
+# the loops of brainstorm/handlers/_cpuop.pyx in numpy, keeping the reference's
+# order of floating-point additions (per image GEMMs; window pixels scanned row by
+# row; output windows visited row by row).
+# --------------------------------------------------------------------------
+def _im2col_one(img, kh, kw, pad, sy, sx):
+    """(oh*ow, kh*kw*C) patch matrix of one (H, W, C) image, _cpuop.pyx:251-280."""
+    H, W, C = img.shape
+    oh = (H + 2 * pad - kh) // sy + 1
+    ow = (W + 2 * pad - kw) // sx + 1
+    padded = np.zeros((H + 2 * pad, W + 2 * pad, C), img.dtype)
+    padded[pad:pad + H, pad:pad + W] = img
+    col = np.zeros((oh, ow, kh, kw, C), img.dtype)
+    for ky in range(kh):
+        for kx in range(kw):
+            col[:, :, ky, kx, :] = padded[ky:ky + sy * oh:sy, kx:kx + sx * ow:sx]
+    return col.reshape(oh * ow, kh * kw * C), oh, ow
+
+
+def _conv2d_forward_batch(self, inputs, weights, bias, outputs, padding, stride):
+    F = weights.shape[0]
+    w2 = weights.reshape(F, -1)
+    for i in range(inputs.shape[0]):                        # numpy_handler.py:158-169
+        col, oh, ow = _im2col_one(inputs[i], weights.shape[1], weights.shape[2], padding, stride[0], stride[1])
+        outputs[i].reshape(oh * ow, F)[...] = np.dot(col, w2.T)
+    outputs += bias.reshape((1, 1, 1, F))                   # :171
+
+
+def _conv2d_backward_batch(self, inputs, params, padding, stride, in_deltas, out_deltas, dparams, dbias):
+    F, kh, kw, C = params.shape
+    H, W = inputs.shape[1], inputs.shape[2]
+    p2 = params.reshape(F, -1)
+    dparams.fill(0.0)                                       # numpy_handler.py:118-119
+    dbias.fill(0.0)
+    for i in range(inputs.shape[0]):
+        col, oh, ow = _im2col_one(inputs[i], kh, kw, padding, stride[0], stride[1])
+        od = out_deltas[i].reshape(oh * ow, F)
+        dparams.reshape(F, -1)[...] += np.dot(od.T, col)    # :135
+        dbias += np.sum(od, axis=0)                         # :137
+        cold = np.dot(od, p2).reshape(oh, ow, kh, kw, C)    # :141
+        padded = np.zeros((H + 2 * padding, W + 2 * padding, C), inputs.dtype)
+        padded[padding:padding + H, padding:padding + W] = in_deltas[i]
+        for oy in range(oh):                                # col2im, _cpuop.pyx:282-309
+            for ox in range(ow):
+                padded[oy * stride[0]:oy * stride[0] + kh, ox * stride[1]:ox * stride[1] + kw] += cold[oy, ox]
+        in_deltas[i] = padded[padding:padding + H, padding:padding + W]
+
+
+def _pool_geometry(inputs, window, outputs, padding, stride):
+    N, H, W, C = inputs.shape
+    return N, H, W, C, window[0], window[1], stride[0], stride[1], outputs.shape[1], outputs.shape[2]
+
+
+def _maxpool2d_forward_batch(self, inputs, window, outputs, padding, stride, argmax):
+    N, H, W, C, kh, kw, sy, sx, oh, ow = _pool_geometry(inputs, window, outputs, padding, stride)
+    lowest = -np.finfo(inputs.dtype).max
+    for oy in range(oh):                                    # _cpuop.pyx:27-82
+        y0, y1 = max(oy * sy - padding, 0), min(oy * sy - padding + kh, H)
+        for ox in range(ow):
+            x0, x1 = max(ox * sx - padding, 0), min(ox * sx - padding + kw, W)
+            best = np.full((N, C), lowest, inputs.dtype)
+            idx = np.full((N, C), -1.0, inputs.dtype)
+            for y in range(y0, y1):
+                for x in range(x0, x1):
+                    v = inputs[:, y, x, :]
+                    better = v > best
+                    best = np.where(better, v, best)
+                    idx = np.where(better, ((y * W + x) * C + np.arange(C)).astype(inputs.dtype), idx)
+            outputs[:, oy, ox, :] = np.where(idx < 0, 0, best)
+            argmax[:, oy, ox, :] = idx
+
+
+def _maxpool2d_backward_batch(self, inputs, window, outputs, padding, stride, argmax, in_deltas, out_deltas):
+    N, H, W, C, kh, kw, sy, sx, oh, ow = _pool_geometry(inputs, window, outputs, padding, stride)
+    flat = in_deltas.reshape(N, H * W * C)
+    for oy in range(oh):                                    # _cpuop.pyx:84-117
+        for ox in range(ow):
+            idx = argmax[:, oy, ox, :].astype(np.int64)
+            n_i, c_i = np.nonzero(idx >= 0)
+            flat[n_i, idx[n_i, c_i]] += out_deltas[n_i, oy, ox, c_i]
+
+
+def _avgpool2d_forward_batch(self, inputs, window, outputs, padding, stride):
+    N, H, W, C, kh, kw, sy, sx, oh, ow = _pool_geometry(inputs, window, outputs, padding, stride)
+    for oy in range(oh):                                    # _cpuop.pyx:120-165
+        y0, y1 = max(oy * sy - padding, 0), min(oy * sy - padding + kh, H)
+        for ox in range(ow):
+            x0, x1 = max(ox * sx - padding, 0), min(ox * sx - padding + kw, W)
+            acc = np.zeros((N, C), inputs.dtype)
+            for y in range(y0, y1):
+                for x in range(x0, x1):
+                    acc = acc + inputs[:, y, x, :]
+            outputs[:, oy, ox, :] = acc / inputs.dtype.type(max((y1 - y0) * (x1 - x0), 1))
+
+
+def _avgpool2d_backward_batch(self, inputs, window, outputs, padding, stride, in_deltas, out_deltas):
+    N, H, W, C, kh, kw, sy, sx, oh, ow = _pool_geometry(inputs, window, outputs, padding, stride)
+    for oy in range(oh):                                    # _cpuop.pyx:167-205
+        y0, y1 = max(oy * sy - padding, 0), min(oy * sy - padding + kh, H)
+        for ox in range(ow):
+            x0, x1 = max(ox * sx - padding, 0), min(ox * sx - padding + kw, W)
+            size = (y1 - y0) * (x1 - x0)
+            if size > 0:
+                in_deltas[:, y0:y1, x0:x1, :] += (out_deltas[:, oy, ox, :] /
+                                                  inputs.dtype.type(size))[:, None, None, :]
+
+
+OracleHandler.conv2d_forward_batch = _conv2d_forward_batch
+OracleHandler.conv2d_backward_batch = _conv2d_backward_batch
+OracleHandler.maxpool2d_forward_batch = _maxpool2d_forward_batch
+OracleHandler.maxpool2d_backward_batch = _maxpool2d_backward_batch
+OracleHandler.avgpool2d_forward_batch = _avgpool2d_forward_batch
+OracleHandler.avgpool2d_backward_batch = _avgpool2d_backward_batch

@@ -194,6 +194,52 @@ def build_cases():
                 add(Case('dot_add_mm', [('a', a), ('b', b),
                                         ('out', _randn(rs, (M, N)))],
                          ['a', 'b', 'out'], dict(transa=ta, transb=tb), tag))
+    # convolution and pooling (NHWC), shapes after the reference's own tests
+    # (test_handlers_against_reference.py:478-659) plus strides > 1
+    def out_hw(H, W, kh, kw, pad, st):
+        return (H + 2 * pad - kh) // st[0] + 1, (W + 2 * pad - kw) // st[1] + 1
+
+    for (img, wsh, pad, st) in (((1, 3, 3, 1), (1, 1, 1), 1, (1, 1)), ((3, 8, 8, 1), (3, 3, 3), 1, (1, 1)),
+                                ((2, 6, 4, 3), (6, 2, 2), 1, (1, 1)), ((1, 3, 4, 2), (2, 1, 3), 1, (1, 1)),
+                                ((2, 7, 9, 4), (5, 3, 2), 2, (2, 1)), ((2, 8, 8, 3), (4, 3, 3), 0, (2, 2))):
+        N, H, W, C = img
+        x = _randn(rs, img)
+        w = _uniform(rs, (wsh[0], wsh[1], wsh[2], C), 0.0, 1.0)
+        b = _uniform(rs, (wsh[0],), 0.0, 1.0)
+        oh, ow = out_hw(H, W, wsh[1], wsh[2], pad, st)
+        tag = 'k%dx%d-p%d-s%dx%d' % (wsh[1], wsh[2], pad, st[0], st[1])
+        add(Case('conv2d_forward_batch', [('x', x), ('w', w), ('b', b), ('out', np.zeros((N, oh, ow, wsh[0]), F32))],
+                 ['x', 'w', 'b', 'out', pad, st], tag=tag))
+        add(Case('conv2d_backward_batch',
+                 [('x', x), ('w', w), ('in_deltas', _randn(rs, img)),
+                  ('out_deltas', _uniform(rs, (N, oh, ow, wsh[0]), 0.0, 1.0)),
+                  ('dw', _randn(rs, w.shape)), ('db', _randn(rs, b.shape))],
+                 ['x', 'w', pad, st, 'in_deltas', 'out_deltas', 'dw', 'db'], tag=tag))
+
+    for img in ((1, 5, 5, 1), (1, 8, 8, 3), (3, 6, 4, 2), (1, 6, 9, 2)):
+        N, H, W, C = img
+        x = _randn(rs, img)
+        for pad, st, win in ((0, (1, 1), (2, 2)), (1, (2, 2), (3, 3)), (2, (1, 2), (4, 4)), (0, (2, 1), (2, 1)),
+                             (1, (1, 1), (1, 2)), (2, (2, 2), (2, 2))):
+            oh, ow = out_hw(H, W, win[0], win[1], pad, st)
+            if oh <= 0 or ow <= 0:
+                continue
+            tag = 'w%dx%d-p%d-s%dx%d' % (win[0], win[1], pad, st[0], st[1])
+            oshape = (N, oh, ow, C)
+            add(Case('maxpool2d_forward_batch', [('x', x), ('out', np.zeros(oshape, F32)), ('argmax', np.zeros(oshape, F32))],
+                     ['x', win, 'out', pad, st, 'argmax'], tag=tag))
+            add(Case('avgpool2d_forward_batch', [('x', x), ('out', np.zeros(oshape, F32))],
+                     ['x', win, 'out', pad, st], tag=tag))
+            # backward cases: outputs / argmax of the forward pass are filled in by
+            # finalize_derivs() (reference when generating, stored values when checking)
+            add(Case('maxpool2d_backward_batch',
+                     [('x', x), ('out', np.zeros(oshape, F32)), ('argmax', np.zeros(oshape, F32)),
+                      ('in_deltas', _randn(rs, img)), ('out_deltas', _randn(rs, oshape))],
+                     ['x', win, 'out', pad, st, 'argmax', 'in_deltas', 'out_deltas'], tag=tag))
+            add(Case('avgpool2d_backward_batch',
+                     [('x', x), ('out', np.zeros(oshape, F32)), ('in_deltas', _randn(rs, img)),
+                      ('out_deltas', _randn(rs, oshape))],
+                     ['x', win, 'out', pad, st, 'in_deltas', 'out_deltas'], tag=tag))
     return cases
 
 
@@ -208,6 +254,11 @@ def finalize_derivs(cases, handler_factory, wrap=lambda h, x: x,
             y = np.zeros_like(c.arrays['x'])
             getattr(h, act)(c.arrays['x'].copy(), y)
             c.arrays['y'] = y
+        elif c.op == 'maxpool2d_backward_batch':
+            x, win, _, pad, st = [c.arrays[a] if isinstance(a, str) else a for a in c.call[:5]]
+            out, am = np.zeros_like(c.arrays['out']), np.zeros_like(c.arrays['argmax'])
+            h.maxpool2d_forward_batch(x.copy(), win, out, pad, st, am)
+            c.arrays['out'], c.arrays['argmax'] = out, am
     return cases
 
 
@@ -218,7 +269,8 @@ def inputs_digest(cases):
     hsh = hashlib.sha256()
     for c in cases:
         for k, v in c.arrays.items():
-            if k == 'y' and c.op.endswith('_deriv'):
+            if (k == 'y' and c.op.endswith('_deriv')) or \
+                    (k in ('out', 'argmax') and c.op == 'maxpool2d_backward_batch'):
                 continue
             hsh.update(np.ascontiguousarray(v).tobytes())
     return hsh.hexdigest()

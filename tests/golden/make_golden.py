@@ -38,7 +38,9 @@ def main():
             before = c.arrays[name]
             changed = not np.array_equal(before.view(np.uint32),
                                          after.view(np.uint32))
-            if changed or (name == 'y' and c.op.endswith('_deriv')):
+            derived_input = (name == 'y' and c.op.endswith('_deriv')) or \
+                (name in ('out', 'argmax') and c.op == 'maxpool2d_backward_batch')
+            if changed or derived_input:
                 store['%d/%s' % (i, name)] = after
     # host-RNG parity mode: masks / gaussians drawn from a seeded RandomState
     # exactly as numpy_handler.py:193-200 does.

@@ -13,7 +13,8 @@ ELEMENTWISE_RTOL = 1e-6
 REDUCTION_RTOL = 1e-5
 
 BIT_EXACT_OPS = {'binarize_v', 'index_m_by_v', 'fill', 'copy_to', 'copy_to_if', 'fill_if',
-                 'broadcast_t', 'merge_tt', 'abs_t', 'sign_t', 'clip_t', 'rel', 'rel_deriv'}
+                 'broadcast_t', 'merge_tt', 'abs_t', 'sign_t', 'clip_t', 'rel', 'rel_deriv',
+                 'maxpool2d_forward_batch'}
 ABS_FLOOR = {'el': 5e-7, 'el_deriv': 5e-7, 'modulo_tt': 0.0}
 
 
@@ -68,7 +69,12 @@ def reduction_scale(op, arrays, kwargs, call):
         return s
     if op == 'softmax_m':
         return 1.0
+    if op.startswith(('conv2d', 'avgpool2d', 'maxpool2d')):
+        # sums of a few dozen terms of order one: one scale for all outputs
+        return float(max(np.abs(v).max() for v in arrays.values() if v.size) *
+                     max(np.prod(arrays['w'].shape[1:]) if 'w' in arrays else 16, 16))
     raise KeyError(op)
 
 
-REDUCTION_OPS = {'sum_t', 'dot_mm', 'dot_add_mm', 'softmax_m'}
+REDUCTION_OPS = {'sum_t', 'dot_mm', 'dot_add_mm', 'softmax_m', 'conv2d_forward_batch', 'conv2d_backward_batch',
+                 'avgpool2d_forward_batch', 'avgpool2d_backward_batch', 'maxpool2d_backward_batch'}

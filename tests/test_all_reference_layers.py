@@ -2,7 +2,7 @@
 31 layer factories x 4 (time, batch, activation) specs), set up exactly as the
 reference's own helper does (tests/helpers.py:45-76), run forward and backward on
 B200Handler and on NumpyHandler(float32) with identical values, all buffers
-compared.  Convolution and pooling are not part of this backend and must say so."""
+compared, convolution and pooling layers included."""
 import numpy as np
 import pytest
 
@@ -16,8 +16,6 @@ if has_reference():
     SPECS = ref_tests.spec_list
 else:                                                   # collected, then skipped
     FACTORIES, SPECS = [], []
-
-NOT_BUILT = ('convolution', 'pooling')
 
 
 def _set_up(layer, spec, handler, seed):
@@ -65,10 +63,6 @@ def test_layer_forward_backward_matches_numpy_handler(factory, spec):
     from brainstorm.handlers import NumpyHandler
     from brainstorm_b200 import B200Handler
     gpu = B200Handler(seed=3, rng_mode='host')
-    if any(k in factory.__name__ for k in NOT_BUILT):
-        with pytest.raises(NotImplementedError):
-            _run(factory, spec, gpu)
-        return
     want = _run(factory, spec, NumpyHandler(np.float32, seed=3))
     got = _run(factory, spec, gpu)
     assert set(got) == set(want)
