@@ -267,3 +267,35 @@ def test_overlapped_upload_orders_with_compute(H):
     assert np.array_equal(first, 2 * src0) and np.array_equal(second, 2 * src1)
     with pytest.raises(ValueError):
         H.upload_async(buf, np.zeros(n - 1, np.float32))
+
+
+def test_zero_size_operands_are_no_ops(H):
+    """The memory layer first creates every time/batch-sized buffer for a 0 x 0 batch
+    (buffers.py:67,108): every op must accept empty operands."""
+    for shape in ((0, 5), (3, 0), (1, 0, 7)):
+        a, b, out = H.zeros(shape), H.zeros(shape), H.zeros(shape)
+        H.add_tt(a, b, out)
+        H.mult_st(2.0, a, out)
+        H.sigmoid(a, out)
+        H.tanh_deriv(None, a, b, out)
+        H.fill(out, 1.0)
+        H.copy_to(a, out)
+        assert H.get_numpy_copy(out).shape == shape
+        assert H.is_fully_finite(a)
+    m = H.zeros((0, 5))
+    H.add_mv(m, H.ones((1, 5)), m)
+    H.softmax_m(m, m)
+    s = H.ones((1, 5))
+    H.sum_t(m, 0, s)                       # the empty sum is 0
+    assert not H.get_numpy_copy(s).any()
+    tot = H.ones(())
+    H.sum_t(m, None, tot)
+    assert float(H.get_numpy_copy(tot)) == 0.0
+    H.binarize_v(H.zeros((0, 1)), m)
+    H.index_m_by_v(m, H.zeros((0, 1)), H.zeros((0, 1)))
+    out = H.ones((4, 3))
+    H.dot_mm(H.zeros((4, 0)), H.zeros((0, 3)), out)      # empty contraction: zeros
+    assert not H.get_numpy_copy(out).any()
+    H.dot_add_mm(H.zeros((4, 0)), H.zeros((0, 3)), out)
+    H.dot_mm(H.zeros((0, 6)), H.zeros((6, 3)), H.zeros((0, 3)))
+    H.synchronize()
