@@ -554,13 +554,11 @@ def run_b200(args):
             pass
         dom = 'add_tt'
         achieved = nbytes[dom] / (op_ms[dom] * 1e-3) / 1e9
-        cpu = None
-        if world == 1 or True:
-            threads = os.cpu_count() or 1
-            cgbs, cdt, ckind = cpu_suite_time(CPU_SAMPLE_ROWS, COLS, SEED, threads, 2, 1)
-            cpu = {'value': round(cgbs, 3), 'unit': UNIT, 'cores': threads, 'kind': ckind,
-                   'sample': '%d of %d rows per step (same %d columns, same ops), 2 steps after 1 warm-up, '
-                             'row chunks over %d threads' % (CPU_SAMPLE_ROWS, ROWS, COLS, threads)}
+        threads = os.cpu_count() or 1
+        cgbs, cdt, ckind = cpu_suite_time(CPU_SAMPLE_ROWS, COLS, SEED, threads, 2, 1)
+        cpu = {'value': round(cgbs, 3), 'unit': UNIT, 'cores': threads, 'kind': ckind,
+               'sample': '%d of %d rows per step (same %d columns, same ops), 2 steps after 1 warm-up, '
+                         'row chunks over %d threads' % (CPU_SAMPLE_ROWS, ROWS, COLS, threads)}
         line = {
             'metric': METRIC, 'value': round(value, 1), 'unit': UNIT, 'n_gpus': world,
             'steps': args.steps, 'warmup': max(args.warmup, 3), 'ms_per_step': round(ms_per_step, 4),
