@@ -78,23 +78,26 @@ sum_axis0_pass1(const float* a, int64_t rows, int64_t cols, int64_t ld, int64_t 
   const int64_t r_lo = (int64_t)blockIdx.y * rows_per_chunk;
   int64_t r_hi = r_lo + rows_per_chunk;
   if (r_hi > rows) r_hi = rows;
-  float acc[4][W];
+  constexpr int U = 8;   // rows in flight per thread
+  float acc[U][W];
 #pragma unroll
-  for (int u = 0; u < 4; ++u)
+  for (int u = 0; u < U; ++u)
 #pragma unroll
     for (int w = 0; w < W; ++w) acc[u][w] = 0.f;
   if (c < cols) {
     int64_t r = r_lo + ty;
-    for (; r + 24 < r_hi; r += 32) {
+    for (; r + 8 * (U - 1) < r_hi; r += 8 * U) {
+      float4 v[U];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < U; ++u) {
         const float* p = a + (r + 8 * u) * ld + c;
-        if (VEC) {
-          const float4 v = __ldcs(reinterpret_cast<const float4*>(p));
-          acc[u][0] += v.x; acc[u][1 % W] += v.y; acc[u][2 % W] += v.z; acc[u][3 % W] += v.w;
-        } else {
-          acc[u][0] += __ldcs(p);
-        }
+        if (VEC) v[u] = __ldcs(reinterpret_cast<const float4*>(p));
+        else v[u] = make_float4(__ldcs(p), 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        acc[u][0] += v[u].x;
+        if (VEC) { acc[u][1 % W] += v[u].y; acc[u][2 % W] += v[u].z; acc[u][3 % W] += v[u].w; }
       }
     }
     for (; r < r_hi; r += 8) {
@@ -109,7 +112,8 @@ sum_axis0_pass1(const float* a, int64_t rows, int64_t cols, int64_t ld, int64_t 
   }
 #pragma unroll
   for (int w = 0; w < W; ++w)
-    smem[ty][tx * W + w] = (acc[0][w] + acc[1][w]) + (acc[2][w] + acc[3][w]);
+    smem[ty][tx * W + w] = ((acc[0][w] + acc[1][w]) + (acc[2][w] + acc[3][w])) +
+                           ((acc[4][w] + acc[5][w]) + (acc[6][w] + acc[7][w]));
   __syncthreads();
   // 32*W columns, summed over the 8 row lanes in a fixed order
   for (int j = ty * 32 + tx; j < 32 * W; j += 256) {
