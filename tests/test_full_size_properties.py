@@ -117,3 +117,30 @@ def test_broadcast_linearity(world):
     parity.assert_elementwise_close(_rows(H, out, rows), ha * hcol[rows], 'mult_mv')
     H.mult_st(0.37, a, out)
     parity.assert_elementwise_close(_rows(H, out, rows), np.float32(0.37) * ha, 'mult_st')
+
+
+def test_more_than_2_to_31_elements():
+    """64-bit indexing: a flat array of 2^31 + 5 elements (8 GiB) through the
+    elementwise, scalar and reduction kernels."""
+    from brainstorm_b200 import B200Handler
+    H = B200Handler(seed=2)
+    n = (1 << 31) + 5
+    a, out = H.allocate((n,)), H.allocate((n,))
+    H.fill(a, 0.5)
+    H.mult_st(3.0, a, out)              # 1.5 everywhere
+    H.add_tt(out, a, out)               # 2.0 everywhere, in place
+    tail = H.get_numpy_copy(out[n - 7:])
+    assert tail.tolist() == [2.0] * 7
+    head = H.get_numpy_copy(out[:3])
+    assert head.tolist() == [2.0] * 3
+    total = H.zeros(())
+    H.sum_t(out, None, total)
+    # every partial is exactly representable; the total rounds to the nearest float32 (ulp 512 at 2^32)
+    assert float(H.get_numpy_copy(total)) == float(np.float32(2.0 * n))
+    m = out[:(1 << 31)].reshape((1 << 20, 1 << 11))
+    s1 = H.zeros((1 << 20, 1))
+    H.sum_t(m, 1, s1)
+    assert np.array_equal(H.get_numpy_copy(s1), np.full((1 << 20, 1), 4096.0, np.float32))
+    s0 = H.zeros((1, 1 << 11))
+    H.sum_t(m, 0, s0)
+    assert np.array_equal(H.get_numpy_copy(s0), np.full((1, 1 << 11), float(1 << 21), np.float32))
