@@ -548,7 +548,7 @@ def run_b200(args):
             peak = 6650.0
         traffic = None
         try:
-            with open(os.path.join(ROOT, 'profiles', 'ncu_traffic.json')) as f:
+            with open(os.path.join(ROOT, 'profiles', 'ncu_traffic.txt')) as f:
                 traffic = json.load(f).get('ew_flat_vec_add_tt_bytes_per_launch_1gib')
         except Exception:
             pass
