@@ -182,3 +182,28 @@ def test_reference_trainer_with_iterators_and_hooks():
     np.testing.assert_allclose(logs[1][0], logs[0][0], rtol=2e-4)
     np.testing.assert_allclose(logs[1][1], logs[0][1], rtol=2e-4)
     _close_l2(logs[1][2], logs[0][2], 1e-3, 'parameters after 3 epochs')
+
+
+def test_device_one_hot_iterator_matches_host_one_hot():
+    """Trainer + DeviceOneHot (indices uploaded, one-hot rows written on the GPU)
+    against Trainer + the reference's host OneHot on NumpyHandler."""
+    import brainstorm as bs
+    from brainstorm.handlers import NumpyHandler
+    from brainstorm_b200 import B200Handler, workloads
+    from brainstorm_b200.iterators import DeviceOneHot
+    rs = np.random.RandomState(2)
+    T, B, V = 5, 8, 9
+    idx = rs.randint(0, V, (T, 2 * B, 1))
+    tgt = rs.randint(0, V, (T, 2 * B, 1)).astype(np.int32)
+    results = []
+    for handler, onehot in ((NumpyHandler(np.float32), bs.data_iterators.OneHot),
+                            (B200Handler(seed=1), DeviceOneHot)):
+        net, _, _ = workloads.lstm(time=T, batch=B, vocab=V, hidden=12, layers=1)
+        net.set_handler(handler)
+        trainer = bs.Trainer(bs.training.SgdStepper(learning_rate=0.1), verbose=False)
+        trainer.add_hook(bs.hooks.StopAfterEpoch(2))
+        it = onehot(bs.data_iterators.Minibatches(B, shuffle=False, default=idx, targets=tgt), {'default': V})
+        trainer.train(net, it)
+        results.append((trainer.logs['rolling_training']['total_loss'], net.get('parameters')))
+    np.testing.assert_allclose(results[1][0], results[0][0], rtol=1e-4)
+    _close(results[1][1], results[0][1], 2e-4, 'parameters')
