@@ -166,6 +166,8 @@ struct TcConfig {
   // drain warps [128, 256)); narrower tiles by the drain warps alone.
   static constexpr int DRAIN_GROUPS = (BN > 128) ? 2 : 1;
   static constexpr int ACC = BN / DRAIN_GROUPS;
+  // the epilogue stages each warp's 32 x ACC tile (padded) in the then idle stage memory
+  static_assert(4 * DRAIN_GROUPS * 32 * (ACC + 4) * 4 <= STAGES * STAGE_BYTES, "epilogue staging does not fit");
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 };
 
@@ -186,30 +188,40 @@ __device__ __forceinline__ void drain_add(uint32_t taddr, float (&acc)[NCOLS]) {
   }
 }
 
-// one output row segment: crow[col0 + j] (+)= acc[j], j < NCOLS, columns >= N masked
+// Epilogue of one warp: its 32 rows x NCOLS accumulators (one row per lane) go to
+// c[(row0 + r) * ldc + col0 + j] (+= when accumulating).  A lane-per-row store would
+// touch 32 different lines per instruction and serialise in the load/store unit, so
+// the tile is first transposed through shared memory (sbuf: 32 x (NCOLS + 4) floats,
+// conflict-free) and then written row by row with whole-line stores.
 template <int NCOLS>
-__device__ __forceinline__ void store_row(const float (&acc)[NCOLS], float* crow, int col0, int N,
-                                          int accumulate, bool vec_ok) {
+__device__ __forceinline__ void store_tile(const float (&acc)[NCOLS], float* sbuf, float* c, int64_t ldc,
+                                           int row0, int col0, int M, int N, int accumulate) {
+  constexpr int LD = NCOLS + 4;
+  constexpr int V = NCOLS / 4;               // float4 groups per row
+  const int lane = threadIdx.x & 31;
 #pragma unroll
-  for (int cc = 0; cc < NCOLS / 32; ++cc) {
-    const int c0 = col0 + cc * 32;
-    if (vec_ok && c0 + 32 <= N) {
-#pragma unroll
-      for (int j = 0; j < 32; j += 4) {
-        float4 o = make_float4(acc[cc * 32 + j], acc[cc * 32 + j + 1], acc[cc * 32 + j + 2], acc[cc * 32 + j + 3]);
-        float4* p = reinterpret_cast<float4*>(crow + c0 + j);
-        if (accumulate) {
-          const float4 old = *p;
-          o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-        }
-        *p = o;
+  for (int j = 0; j < NCOLS; j += 4)
+    *reinterpret_cast<float4*>(sbuf + lane * LD + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+  __syncwarp();
+  const bool vec_ok = ((reinterpret_cast<uintptr_t>(c) & 15) == 0) && (ldc % 4 == 0);
+#pragma unroll 4
+  for (int idx = lane; idx < 32 * V; idx += 32) {
+    const int r = idx / V, g = idx - r * V;
+    const int row = row0 + r, col = col0 + 4 * g;
+    if (row >= M || col >= N) continue;
+    float4 o = *reinterpret_cast<const float4*>(sbuf + r * LD + 4 * g);
+    float* p = c + (int64_t)row * ldc + col;
+    if (vec_ok && col + 4 <= N) {
+      if (accumulate) {
+        const float4 old = *reinterpret_cast<const float4*>(p);
+        o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
       }
+      *reinterpret_cast<float4*>(p) = o;
     } else {
+      const float v[4] = {o.x, o.y, o.z, o.w};
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const int col = c0 + j;
-        if (col < N) crow[col] = accumulate ? crow[col] + acc[cc * 32 + j] : acc[cc * 32 + j];
-      }
+      for (int j = 0; j < 4; ++j)
+        if (col + j < N) p[j] = accumulate ? p[j] + v[j] : v[j];
     }
   }
 }
@@ -412,11 +424,10 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         mbar_arrive(acc_empty_bar(buf));
       }
       if (ok) {
-        const int row = m0 + q * 32 + lane;
-        const bool vec_ok = ((reinterpret_cast<uintptr_t>(c) & 15) == 0) && (ldc % 4 == 0);
-        if (row < M)
-          store_row<kDrainsToo ? Cfg::ACC : 32>(*reinterpret_cast<float(*)[kDrainsToo ? Cfg::ACC : 32]>(acc),
-                                                c + (int64_t)row * ldc, n0, N, accumulate, vec_ok);
+        // every MMA has completed (last chunk drained): the stage memory is free to stage the tile
+        constexpr int NC = kDrainsToo ? Cfg::ACC : 32;
+        float* sbuf = reinterpret_cast<float*>(smem) + (warp - 2) * 32 * (NC + 4);
+        store_tile<NC>(*reinterpret_cast<float(*)[NC]>(acc), sbuf, c, ldc, m0 + q * 32, n0, M, N, accumulate);
       }
     }
   } else {
@@ -440,9 +451,11 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       mbar_arrive(acc_empty_bar(buf));
     }
     if (ok) {
-      const int row = m0 + q * 32 + lane;
-      const bool vec_ok = ((reinterpret_cast<uintptr_t>(c) & 15) == 0) && (ldc % 4 == 0);
-      if (row < M) store_row<Cfg::ACC>(acc, c + (int64_t)row * ldc, n0 + COL0, N, accumulate, vec_ok);
+      // every MMA has completed (last chunk drained): the stage memory is free to stage the tile;
+      // with two drain groups the transform warps use the first four slots
+      constexpr int SLOT0 = (Cfg::DRAIN_GROUPS == 2) ? 4 : 0;
+      float* sbuf = reinterpret_cast<float*>(smem) + (SLOT0 + warp - 6) * 32 * (Cfg::ACC + 4);
+      store_tile<Cfg::ACC>(acc, sbuf, c, ldc, m0 + q * 32, n0 + COL0, M, N, accumulate);
     }
   }
   tc_fence_before();
