@@ -353,6 +353,22 @@ def other_training_configs(H, rank, lib, only=None):
         batch = data['default'].shape[1]
         out[name] = {'samples_per_s': round(batch / dt, 1), 'ms_per_step': round(dt * 1e3, 3), 'batch': batch,
                      'gpu_launches_per_step': int((lib.b200_launch_count() - l0) // steps)}
+        if name == 'mlp':
+            # the same step replayed from a recording (one launch call per step)
+            from brainstorm_b200 import GraphedStepper
+            st = GraphedStepper(stepper(), eager_steps=1)
+            st.start(net)
+            for _ in range(3):
+                step()
+            H.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(steps):
+                step()
+            H.synchronize()
+            dt = (time.perf_counter() - t0) / steps
+            out[name]['recorded_ms_per_step'] = round(dt * 1e3, 3)
+            out[name]['recorded_samples_per_s'] = round(batch / dt, 1)
+            st.invalidate()
         del net
     return out
 

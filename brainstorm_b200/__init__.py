@@ -7,9 +7,10 @@ The first use of any name below loads ``libb200handler.so`` (build it with
 ``python -m brainstorm_b200.build``); there is no CPU fallback.  The names are
 resolved lazily so that the build module can be run before the library exists.
 """
-__all__ = ['B200Handler', 'B200Array', 'B200Error', 'lib']
+__all__ = ['B200Handler', 'B200Array', 'B200Error', 'GraphedStepper', 'RecordedStep', 'lib']
 
-_HOME = {'B200Handler': 'handler', 'B200Array': 'array', 'B200Error': '_lib', 'lib': '_lib'}
+_HOME = {'B200Handler': 'handler', 'B200Array': 'array', 'B200Error': '_lib', 'lib': '_lib',
+         'GraphedStepper': 'graph', 'RecordedStep': 'graph'}
 
 
 def __getattr__(name):

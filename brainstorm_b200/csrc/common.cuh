@@ -28,6 +28,16 @@ int cuda_fail(cudaError_t e, const char* what, const char* file, int line);
     if (e__ != cudaSuccess) return b200::cuda_fail(e__, #call, __FILE__, __LINE__); \
   } while (0)
 
+// For entry points that wait for the device or move data across PCIe: these cannot
+// become nodes of a recorded graph.
+#define B200_NOT_WHILE_RECORDING(what)                                                        \
+  do {                                                                                        \
+    if (b200::state().capturing)                                                              \
+      return b200::set_error(B200_ERR_UNSUPPORTED,                                            \
+                             what " is not possible while a graph is being recorded "         \
+                             "(between b200_graph_begin and b200_graph_end)");                \
+  } while (0)
+
 #define B200_REQUIRE(cond, ...)                                                \
   do {                                                                         \
     if (!(cond)) return b200::set_error(B200_ERR_ARG, __VA_ARGS__);            \
@@ -55,6 +65,9 @@ struct State {
   int gemm_bn = 0;    // 0 = auto, else forced tile width (32/64/128/256)
   int use_pdl = 1;    // programmatic dependent launch inside the LSTM time loops
   bool pdl_now = false;  // set while a time loop is issuing its kernels
+  // graph recording (b200_graph_begin .. b200_graph_end)
+  bool capturing = false;
+  uint64_t* replay_epoch = nullptr;  // device word, advanced before every graph replay
 };
 State& state();
 int require_ready();

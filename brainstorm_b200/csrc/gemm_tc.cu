@@ -691,6 +691,9 @@ static int gemm_tc_impl(int transa, int transb, int64_t M, int64_t N, int64_t K,
     const size_t need = (size_t)splits * split_stride * sizeof(float);
     TcHost& h = tc_host();
     if (h.partial_bytes < need) {
+      // the buffer outlives the call, so it must not become an allocation of a recorded graph
+      B200_REQUIRE(!s.capturing, "the split-K work buffer would have to grow while a graph is being recorded: "
+                                 "run the step once before recording it");
       if (h.partial) B200_CUDA(cudaFreeAsync(h.partial, s.stream));
       h.partial = nullptr;
       h.partial_bytes = 0;

@@ -23,7 +23,11 @@ __device__ __forceinline__ float u01(uint32_t x) { return (float)(x >> 8) * (1.0
 
 // mode 0: out = (u < p0) ? 1 : 0   mode 1: out = p0 + p1 * normal
 __global__ void __launch_bounds__(256)
-rng_kernel(float* out, int64_t n, float p0, float p1, uint64_t seed, uint64_t offset, int mode) {
+rng_kernel(float* out, int64_t n, float p0, float p1, uint64_t seed, uint64_t offset, int mode,
+           const uint64_t* __restrict__ replay_epoch) {
+  // Inside a recorded graph the arguments are frozen; the replay counter (upper half of
+  // the call offset, which counts calls and stays far below 2^32) makes every replay a new stream.
+  if (replay_epoch) offset += *replay_epoch << 32;
   const uint2 key = make_uint2((uint32_t)seed, (uint32_t)(seed >> 32));
   const int64_t groups = (n + 3) >> 2;
   for (int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; g < groups;
@@ -61,7 +65,8 @@ static int launch_rng(float* out, int64_t n, float p0, float p1, uint64_t seed, 
   const State& s = state();
   int64_t blocks = ceil_div(ceil_div(n, 4), 256);
   if (blocks > (int64_t)s.sm_count * 8) blocks = (int64_t)s.sm_count * 8;
-  rng_kernel<<<(unsigned)blocks, 256, 0, s.stream>>>(out, n, p0, p1, seed, offset, mode);
+  rng_kernel<<<(unsigned)blocks, 256, 0, s.stream>>>(out, n, p0, p1, seed, offset, mode,
+                                                     s.capturing ? s.replay_epoch : nullptr);
   B200_LAUNCH_CHECK();
   return B200_OK;
 }

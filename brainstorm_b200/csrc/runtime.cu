@@ -5,6 +5,8 @@
 #include <stdarg.h>
 #include <string.h>
 
+#include <vector>
+
 #include "common.cuh"
 
 namespace b200 {
@@ -41,6 +43,19 @@ int require_ready() {
 }  // namespace b200
 
 using namespace b200;
+
+namespace {
+struct RecordedGraph {
+  cudaGraphExec_t exec = nullptr;
+  uint64_t kernels = 0;            // kernel launches recorded (for b200_launch_count)
+  std::vector<void*> owned;        // arrays released by the host during the recording
+};
+struct Recording {
+  cudaStream_t side_stream = nullptr;
+  std::vector<void*> deferred;
+  uint64_t launches_at_begin = 0;
+} g_rec;
+}  // namespace
 
 B200_API const char* b200_last_error(void) { return g_err; }
 
@@ -111,7 +126,15 @@ B200_API int b200_malloc(uint64_t* ptr, uint64_t bytes, int zero) {
   // Zero-byte arrays are routine (buffers are first created for a 0x0 batch);
   // give them a real, distinct address.
   size_t n = bytes ? (size_t)bytes : 16;
-  B200_CUDA(cudaMallocAsync(&p, n, state().stream));
+  if (state().capturing) {
+    // An allocation on the recording stream would belong to the graph.  The array has
+    // to exist outside it as well (the caller may keep it), so it is made on a side
+    // stream, for real and at once; only the zero fill is recorded.
+    B200_CUDA(cudaMallocAsync(&p, n, g_rec.side_stream));
+    B200_CUDA(cudaStreamSynchronize(g_rec.side_stream));
+  } else {
+    B200_CUDA(cudaMallocAsync(&p, n, state().stream));
+  }
   if (zero) B200_CUDA(cudaMemsetAsync(p, 0, n, state().stream));
   *ptr = (uint64_t)(uintptr_t)p;
   return B200_OK;
@@ -119,7 +142,112 @@ B200_API int b200_malloc(uint64_t* ptr, uint64_t bytes, int zero) {
 
 B200_API int b200_free(uint64_t ptr) {
   if (!state().ready || ptr == 0) return B200_OK;
+  if (state().capturing) {
+    // the recorded kernels keep using this address on every replay: the memory
+    // stays allocated for as long as the graph exists
+    g_rec.deferred.push_back((void*)(uintptr_t)ptr);
+    return B200_OK;
+  }
   B200_CUDA(cudaFreeAsync((void*)(uintptr_t)ptr, state().stream));
+  return B200_OK;
+}
+
+// ---- recorded graphs -------------------------------------------------------------------
+// b200_graph_begin() puts the library stream into capture mode: every kernel, fill
+// and device-to-device copy issued through this library until b200_graph_end() is
+// recorded instead of executed.  The result replays with one call
+// (b200_graph_launch), which removes the per-kernel launch cost of steps made of
+// many small kernels.  All addresses and scalar arguments are frozen into the graph.
+// Random masks are the exception: the RNG kernels add a device-side replay counter
+// to their Philox counter, so every replay draws fresh numbers.
+__global__ void advance_epoch_kernel(uint64_t* epoch) { *epoch += 1; }
+
+B200_API int b200_graph_begin(void) {
+  if (int rc = require_ready()) return rc;
+  State& s = state();
+  B200_REQUIRE(!s.capturing, "a graph is already being recorded");
+  if (!g_rec.side_stream) B200_CUDA(cudaStreamCreateWithFlags(&g_rec.side_stream, cudaStreamNonBlocking));
+  if (!s.replay_epoch) {
+    B200_CUDA(cudaMalloc((void**)&s.replay_epoch, sizeof(uint64_t)));
+    B200_CUDA(cudaMemsetAsync(s.replay_epoch, 0, sizeof(uint64_t), s.stream));
+  }
+  // work queued so far must not be overtaken by allocations made on the side stream
+  B200_CUDA(cudaStreamSynchronize(s.stream));
+  if (int rc = gemm_tc_check_flag()) return rc;
+  g_rec.deferred.clear();
+  g_rec.launches_at_begin = s.launches;
+  B200_CUDA(cudaStreamBeginCapture(s.stream, cudaStreamCaptureModeRelaxed));
+  s.capturing = true;
+  return B200_OK;
+}
+
+static void release_all(std::vector<void*>& ptrs) {
+  for (void* p : ptrs) cudaFreeAsync(p, state().stream);
+  ptrs.clear();
+}
+
+// Ends the recording.  With graph == NULL the recording is discarded.
+B200_API int b200_graph_end(uint64_t* graph) {
+  State& s = state();
+  B200_REQUIRE(s.capturing, "no graph is being recorded");
+  s.capturing = false;
+  cudaGraph_t g = nullptr;
+  const cudaError_t e = cudaStreamEndCapture(s.stream, &g);
+  const uint64_t recorded = s.launches - g_rec.launches_at_begin;
+  s.launches = g_rec.launches_at_begin;   // recorded kernels have not run
+  if (e != cudaSuccess || g == nullptr || graph == nullptr) {
+    if (g) cudaGraphDestroy(g);
+    release_all(g_rec.deferred);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return cuda_fail(e, "cudaStreamEndCapture", __FILE__, __LINE__);
+    }
+    if (graph == nullptr) return B200_OK;
+    return set_error(B200_ERR_CUDA, "the recording produced no graph");
+  }
+  cudaGraphExec_t exec = nullptr;
+  const cudaError_t ei = cudaGraphInstantiate(&exec, g, 0);
+  cudaGraphDestroy(g);
+  if (ei != cudaSuccess) {
+    release_all(g_rec.deferred);
+    return cuda_fail(ei, "cudaGraphInstantiate", __FILE__, __LINE__);
+  }
+  RecordedGraph* r = new RecordedGraph;
+  r->exec = exec;
+  r->kernels = recorded;
+  r->owned.swap(g_rec.deferred);
+  *graph = (uint64_t)(uintptr_t)r;
+  return B200_OK;
+}
+
+B200_API int b200_graph_launch(uint64_t graph) {
+  if (int rc = require_ready()) return rc;
+  B200_REQUIRE(graph != 0, "graph is NULL");
+  B200_NOT_WHILE_RECORDING("replaying a graph");
+  State& s = state();
+  RecordedGraph* r = (RecordedGraph*)(uintptr_t)graph;
+  advance_epoch_kernel<<<1, 1, 0, s.stream>>>(s.replay_epoch);
+  B200_LAUNCH_CHECK();
+  B200_CUDA(cudaGraphLaunch(r->exec, s.stream));
+  s.launches += r->kernels;
+  return B200_OK;
+}
+
+B200_API int b200_graph_kernel_count(uint64_t graph, uint64_t* kernels) {
+  B200_REQUIRE(graph != 0 && kernels != nullptr, "NULL argument");
+  *kernels = ((RecordedGraph*)(uintptr_t)graph)->kernels;
+  return B200_OK;
+}
+
+B200_API int b200_graph_destroy(uint64_t graph) {
+  if (graph == 0) return B200_OK;
+  RecordedGraph* r = (RecordedGraph*)(uintptr_t)graph;
+  if (state().ready) {
+    // replays still queued use the memory: the frees are ordered after them
+    cudaGraphExecDestroy(r->exec);
+    release_all(r->owned);
+  }
+  delete r;
   return B200_OK;
 }
 
@@ -140,6 +268,7 @@ B200_API int b200_host_free(void* ptr) {
 // caller must keep the source untouched until b200_sync().
 B200_API int b200_memcpy_h2d(uint64_t dst, const void* src, uint64_t bytes) {
   if (int rc = require_ready()) return rc;
+  B200_NOT_WHILE_RECORDING("a host-to-device copy");
   if (bytes == 0) return B200_OK;
   B200_CUDA(cudaMemcpyAsync((void*)(uintptr_t)dst, src, (size_t)bytes, cudaMemcpyHostToDevice,
                             state().stream));
@@ -149,6 +278,7 @@ B200_API int b200_memcpy_h2d(uint64_t dst, const void* src, uint64_t bytes) {
 // Device -> host; returns after the data has arrived (synchronises the stream).
 B200_API int b200_memcpy_d2h(void* dst, uint64_t src, uint64_t bytes) {
   if (int rc = require_ready()) return rc;
+  B200_NOT_WHILE_RECORDING("a device-to-host copy");
   if (bytes) {
     B200_CUDA(cudaMemcpyAsync(dst, (const void*)(uintptr_t)src, (size_t)bytes,
                               cudaMemcpyDeviceToHost, state().stream));
@@ -161,6 +291,7 @@ B200_API int b200_memcpy_d2h(void* dst, uint64_t src, uint64_t bytes) {
 B200_API int b200_memcpy2d_h2d(uint64_t dst, uint64_t dst_pitch, const void* src,
                                uint64_t src_pitch, uint64_t row_bytes, uint64_t rows) {
   if (int rc = require_ready()) return rc;
+  B200_NOT_WHILE_RECORDING("a host-to-device copy");
   if (rows == 0 || row_bytes == 0) return B200_OK;
   B200_CUDA(cudaMemcpy2DAsync((void*)(uintptr_t)dst, dst_pitch, src, src_pitch, row_bytes, rows,
                               cudaMemcpyHostToDevice, state().stream));
@@ -170,6 +301,7 @@ B200_API int b200_memcpy2d_h2d(uint64_t dst, uint64_t dst_pitch, const void* src
 B200_API int b200_memcpy2d_d2h(void* dst, uint64_t dst_pitch, uint64_t src, uint64_t src_pitch,
                                uint64_t row_bytes, uint64_t rows) {
   if (int rc = require_ready()) return rc;
+  B200_NOT_WHILE_RECORDING("a device-to-host copy");
   if (rows && row_bytes) {
     B200_CUDA(cudaMemcpy2DAsync(dst, dst_pitch, (const void*)(uintptr_t)src, src_pitch, row_bytes,
                                 rows, cudaMemcpyDeviceToHost, state().stream));
@@ -189,6 +321,7 @@ static cudaEvent_t g_copy_done = nullptr;
 
 B200_API int b200_upload_async(uint64_t dst, const void* src, uint64_t bytes, uint64_t after_event) {
   if (int rc = require_ready()) return rc;
+  B200_NOT_WHILE_RECORDING("an upload");
   if (!g_copy_stream) {
     B200_CUDA(cudaStreamCreateWithFlags(&g_copy_stream, cudaStreamNonBlocking));
     B200_CUDA(cudaEventCreateWithFlags(&g_copy_done, cudaEventDisableTiming));
@@ -201,6 +334,7 @@ B200_API int b200_upload_async(uint64_t dst, const void* src, uint64_t bytes, ui
 
 B200_API int b200_upload_join(void) {
   if (int rc = require_ready()) return rc;
+  B200_NOT_WHILE_RECORDING("joining the upload stream");
   if (!g_copy_stream) return B200_OK;
   B200_CUDA(cudaEventRecord(g_copy_done, g_copy_stream));
   B200_CUDA(cudaStreamWaitEvent(state().stream, g_copy_done, 0));
@@ -209,6 +343,7 @@ B200_API int b200_upload_join(void) {
 
 B200_API int b200_sync(void) {
   if (int rc = require_ready()) return rc;
+  B200_NOT_WHILE_RECORDING("waiting for the device");
   B200_CUDA(cudaStreamSynchronize(state().stream));
   return gemm_tc_check_flag();
 }
@@ -223,6 +358,7 @@ B200_API int b200_event_create(uint64_t* ev) {
 }
 B200_API int b200_event_record(uint64_t ev) {
   if (int rc = require_ready()) return rc;
+  B200_NOT_WHILE_RECORDING("recording an event");
   B200_CUDA(cudaEventRecord((cudaEvent_t)(uintptr_t)ev, state().stream));
   return B200_OK;
 }

@@ -217,6 +217,13 @@ class B200Handler(Handler):
         check(lib.b200_device_info(_byref(dev), _byref(sms), _byref(free), _byref(total)))
         return dev.value, sms.value, free.value, total.value
 
+    def record(self, fn, *args, **kwargs):
+        """Record the handler calls of ``fn(*args, **kwargs)`` instead of executing
+        them; returns a ``RecordedStep`` whose ``launch()`` replays them with one
+        call (see ``brainstorm_b200.graph``)."""
+        from .graph import record
+        return record(fn, *args, **kwargs)
+
     def synchronize(self):
         check(lib.b200_sync())
         if self._label_check:

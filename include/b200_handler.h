@@ -68,6 +68,24 @@ int b200_memcpy2d_d2h(void* dst, uint64_t dst_pitch, uint64_t src, uint64_t src_
 int b200_upload_async(uint64_t dst, const void* src, uint64_t bytes, uint64_t after_event);
 int b200_upload_join(void);
 
+/* ---- recorded steps: one replay call instead of one launch per kernel -------
+ * The caller side of the path, a training step (TrainingStepper.run,
+ * brainstorm/training/steppers.py:61-70,103-121), is a fixed sequence of handler
+ * calls on fixed buffers.  Between b200_graph_begin and b200_graph_end every kernel,
+ * fill and device-to-device copy of this library is recorded into a CUDA graph
+ * instead of executed; b200_graph_launch replays the whole sequence.  Addresses and
+ * scalar arguments are frozen in the recording; random masks are not: every replay
+ * draws from a new Philox stream.  While recording, calls that wait for the device
+ * or cross PCIe (transfers, uploads, b200_sync, events) fail with an error and
+ * record nothing; arrays allocated are real allocations; arrays released stay
+ * allocated until b200_graph_destroy.  b200_graph_end(NULL) discards the recording.
+ * The reference has no counterpart (its GPU backend launches kernel by kernel). */
+int b200_graph_begin(void);                                               /* synchronises */
+int b200_graph_end(uint64_t* graph);
+int b200_graph_launch(uint64_t graph);
+int b200_graph_kernel_count(uint64_t graph, uint64_t* kernels);
+int b200_graph_destroy(uint64_t graph);
+
 /* ---- CUDA-event timing on the library stream (benchmark support) --------- */
 int b200_event_create(uint64_t* ev);
 int b200_event_record(uint64_t ev);

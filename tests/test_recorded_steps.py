@@ -1,0 +1,241 @@
+"""Recorded steps (B200Handler.record / GraphedStepper): a replay must do exactly
+what the same handler calls do one by one."""
+import numpy as np
+import pytest
+
+from conftest import needs_reference
+
+
+# ------------------------------------------------------------------ no GPU needed
+def test_graph_end_without_begin_is_an_error_not_a_crash():
+    from brainstorm_b200._lib import lib
+    assert lib.b200_graph_end(None) != 0
+    assert b'no graph is being recorded' in lib.b200_last_error()
+
+
+def test_graph_launch_needs_an_initialised_library_or_a_handle():
+    from brainstorm_b200._lib import lib
+    assert lib.b200_graph_launch(0) != 0
+    assert lib.b200_graph_destroy(0) == 0
+
+
+# ------------------------------------------------------------------ GPU
+@pytest.fixture(scope='module')
+def H():
+    from brainstorm_b200 import B200Handler
+    return B200Handler(seed=5)
+
+
+@pytest.mark.gpu
+def test_replay_matches_the_same_calls_issued_one_by_one(H):
+    rs = np.random.RandomState(0)
+    x0 = rs.randn(96, 160).astype(np.float32)
+    x1 = rs.randn(96, 160).astype(np.float32)
+    w = H.create_from_numpy(rs.randn(160, 64).astype(np.float32))
+    row = H.create_from_numpy(rs.randn(1, 64).astype(np.float32))
+    x = H.create_from_numpy(x0)
+    tmp, out = H.zeros((96, 160)), H.zeros((96, 64))
+    total = H.zeros((1, 64))
+
+    def calls():
+        H.tanh(x, tmp)
+        H.dot_mm(tmp, w, out)
+        H.add_mv(out, row, out)
+        H.sigmoid(out, out)
+        H.sum_t(out, 0, total)
+
+    calls()                                   # the ordinary way (also sizes work buffers)
+    want0 = (H.get_numpy_copy(out), H.get_numpy_copy(total))
+    H.set_from_numpy(x, x1)
+    calls()
+    want1 = (H.get_numpy_copy(out), H.get_numpy_copy(total))
+
+    step = H.record(calls)
+    assert step.kernels >= 5
+    H.fill(out, -1.0)                         # nothing ran during the recording
+    assert np.all(H.get_numpy_copy(out) == -1.0)
+    for data, want in ((x0, want0), (x1, want1), (x0, want0)):
+        H.set_from_numpy(x, data)
+        H.fill(out, 0.0)
+        step.launch()
+        assert np.array_equal(H.get_numpy_copy(out), want[0])
+        assert np.array_equal(H.get_numpy_copy(total), want[1])
+    step.release()
+    with pytest.raises(ValueError):
+        step.launch()
+
+
+@pytest.mark.gpu
+def test_launch_counter_counts_the_replayed_kernels(H):
+    from brainstorm_b200._lib import lib
+    a, b = H.ones((8, 8)), H.zeros((8, 8))
+
+    def calls():
+        H.add_tt(a, b, b)
+        H.mult_st(0.5, b, b)
+
+    before = lib.b200_launch_count()
+    step = H.record(calls)
+    assert lib.b200_launch_count() == before          # recorded, not launched
+    assert step.kernels == 2
+    step.launch()
+    assert lib.b200_launch_count() == before + 2 + 1   # + the replay-counter kernel
+    assert np.all(H.get_numpy_copy(b) == 0.5)
+
+
+@pytest.mark.gpu
+def test_calls_that_wait_or_transfer_are_refused_and_the_handler_stays_usable(H):
+    from brainstorm_b200 import B200Error
+    a = H.ones((4, 4))
+
+    for bad in (lambda: H.get_numpy_copy(a),
+                lambda: H.set_from_numpy(a, np.zeros((4, 4), np.float32)),
+                lambda: H.synchronize()):
+        def calls():
+            H.mult_st(2.0, a, a)
+            bad()
+        with pytest.raises(B200Error, match='being recorded'):
+            H.record(calls)
+        # the recording was discarded: nothing ran, ordinary calls work again
+        assert np.all(H.get_numpy_copy(a) == 1.0)
+    H.mult_st(2.0, a, a)
+    assert np.all(H.get_numpy_copy(a) == 2.0)
+
+
+@pytest.mark.gpu
+def test_python_exception_inside_the_recorded_function_discards_the_recording(H):
+    a = H.ones((4, 4))
+
+    def calls():
+        H.mult_st(3.0, a, a)
+        raise KeyError('boom')
+
+    with pytest.raises(KeyError):
+        H.record(calls)
+    assert np.all(H.get_numpy_copy(a) == 1.0)
+    step = H.record(lambda: H.mult_st(3.0, a, a))     # a new recording can start
+    step.launch()
+    assert np.all(H.get_numpy_copy(a) == 3.0)
+
+
+@pytest.mark.gpu
+def test_temporaries_made_and_dropped_while_recording_survive_for_the_replays(H):
+    rs = np.random.RandomState(1)
+    x = H.create_from_numpy(rs.randn(300, 70).astype(np.float32))
+    out = H.zeros((300, 70))
+
+    def calls():
+        t = H.zeros((300, 70))          # allocated inside the recording ...
+        H.mult_tt(x, x, t)
+        H.add_tt(t, x, out)
+        del t                           # ... and released inside it
+
+    step = H.record(calls)
+    xs = H.get_numpy_copy(x)
+    want = xs * xs + xs
+    junk = [H.ones((300, 70)) for _ in range(8)]      # would reuse the temporary's memory if it had been freed
+    for _ in range(3):
+        H.fill(out, 0.0)
+        step.launch()
+        assert np.array_equal(H.get_numpy_copy(out), want)
+    assert all(np.all(H.get_numpy_copy(j) == 1.0) for j in junk)
+
+
+@pytest.mark.gpu
+def test_every_replay_draws_a_new_dropout_mask(H):
+    mask = H.zeros((512, 512))
+    step = H.record(lambda: H.generate_probability_mask(mask, 0.3))
+    seen = []
+    for _ in range(3):
+        step.launch()
+        m = H.get_numpy_copy(mask)
+        assert set(np.unique(m)) <= {0.0, 1.0}
+        assert abs(m.mean() - 0.3) < 0.01
+        seen.append(m)
+    assert not np.array_equal(seen[0], seen[1])
+    assert not np.array_equal(seen[1], seen[2])
+    # and the ordinary call after the replays is a different stream again
+    H.generate_probability_mask(mask, 0.3)
+    assert not any(np.array_equal(H.get_numpy_copy(mask), s) for s in seen)
+
+
+def _train(builder, wrap, steps, fused=False, **kw):
+    from brainstorm_b200 import B200Handler
+    net, data, stepper = builder(**kw)
+    net.set_handler(B200Handler(seed=3))
+    if fused:
+        from brainstorm_b200.fused_lstm import fuse_lstm_layers
+        fuse_lstm_layers(net)
+    st = wrap(stepper())
+    st.start(net)
+    losses = []
+    for i in range(steps):
+        batch = {k: np.roll(v, i, axis=1) for k, v in data.items()}   # a new batch every step
+        net.provide_external_data(batch)
+        st.run()
+        losses.append(float(net.get_loss_values()['total_loss']))
+    return net.get('parameters'), losses, st
+
+
+@pytest.mark.gpu
+@needs_reference
+@pytest.mark.parametrize('fused', [False, True])
+def test_graphed_stepper_trains_the_lstm_bit_for_bit_like_the_plain_stepper(fused):
+    from brainstorm_b200 import GraphedStepper, workloads
+    kw = dict(time=6, batch=64, vocab=48, hidden=128)
+    p_plain, l_plain, _ = _train(workloads.lstm, lambda s: s, 5, fused=fused, **kw)
+    p_graph, l_graph, st = _train(workloads.lstm, GraphedStepper, 5, fused=fused, **kw)
+    assert st._step is not None and st._step.kernels > 10     # steps 3.. were replays
+    assert l_plain == l_graph
+    assert np.array_equal(p_plain, p_graph)
+
+
+@pytest.mark.gpu
+@needs_reference
+def test_graphed_stepper_records_again_when_a_frozen_scalar_or_the_batch_shape_changes():
+    import brainstorm as bs
+    from brainstorm_b200 import B200Handler, GraphedStepper, workloads
+    net, data, _ = workloads.lstm(time=5, batch=16, vocab=20, hidden=32)
+    ref, _, _ = workloads.lstm(time=5, batch=16, vocab=20, hidden=32)
+    net.set_handler(B200Handler(seed=3))
+    ref.set_handler(B200Handler(seed=3))
+    plain = bs.training.SgdStepper(learning_rate=0.1)
+    graphed = GraphedStepper(bs.training.SgdStepper(learning_rate=0.1))
+    plain.start(ref)
+    graphed.start(net)
+    half = {k: v[:, :8] for k, v in data.items()}
+    schedule = [(data, 0.1)] * 3 + [(data, 0.05)] * 3 + [(half, 0.05)] * 3 + [(data, 0.05)] * 2
+    recordings = []
+    for batch, lr in schedule:
+        plain.learning_rate = lr
+        graphed.stepper.learning_rate = lr
+        for n, s in ((ref, plain), (net, graphed)):
+            n.provide_external_data(batch)
+            s.run()
+        if graphed._step is not None and not any(r is graphed._step for r in recordings):
+            recordings.append(graphed._step)
+    assert len(recordings) >= 3
+    assert np.array_equal(net.get('parameters'), ref.get('parameters'))
+
+
+@pytest.mark.gpu
+@needs_reference
+def test_graphed_mlp_with_dropout_learns_and_uses_fresh_masks():
+    from brainstorm_b200 import GraphedStepper, workloads
+    _, losses, st = _train(workloads.mlp, GraphedStepper, 30, batch=100)
+    assert st._step is not None
+    assert np.isfinite(losses).all()
+    assert np.mean(losses[-5:]) < np.mean(losses[:5])
+    # the masks of the replayed steps differ from step to step
+    net, data, stepper = workloads.mlp(batch=100)
+    from brainstorm_b200 import B200Handler
+    net.set_handler(B200Handler(seed=3))
+    gs = GraphedStepper(stepper())
+    gs.start(net)
+    masks = []
+    name = [n for n in net.layers if 'ropout' in n][0]
+    for _ in range(5):
+        net.provide_external_data(data)
+        gs.run()
+        masks.append(net.get('%s.internals.mask' % name))
+    assert not np.array_equal(masks[-1], masks[-2])
