@@ -77,7 +77,8 @@ def test_fused_lstm_entry_points_match_reference_layer(tag):
     d = {k: H_.zeros((T + 1, B, Hs)) for k in d_ref}
     dG = H_.zeros((T + 1, B, 4 * Hs))
     order = ('dZa', 'dZb', 'dIa', 'dIb', 'dFa', 'dFb', 'dOa', 'dOb', 'dCa', 'dCb')
-    check(lib.b200_lstm_backward(up(deltas).ptr, Rst.ptr, pst.ptr, f['Zb'].ptr, f['Ib'].ptr, f['Fb'].ptr,
+    deltas_dev = up(deltas)     # keep alive: the call only takes its address
+    check(lib.b200_lstm_backward(deltas_dev.ptr, Rst.ptr, pst.ptr, f['Zb'].ptr, f['Ib'].ptr, f['Fb'].ptr,
                                  f['Ob'].ptr, f['Ca'].ptr, f['Cb'].ptr, *[d[k].ptr for k in order],
                                  dG.ptr, r_work.ptr, T, B, Hs, 1))
     for k in d:
