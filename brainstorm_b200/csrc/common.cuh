@@ -56,7 +56,9 @@ struct State {
   bool ready = false;
   int device = -1;
   int sm_count = 148;
-  cudaStream_t stream = nullptr;
+  cudaStream_t stream = nullptr;      // the stream work is queued on now: streams[stream_index]
+  cudaStream_t streams[2] = {nullptr, nullptr};   // [0] the library's main stream, [1] the side stream
+  int stream_index = 0;
   uint64_t launches = 0;  // kernels launched by this library so far
   // tuning knobs (b200_set_tuning)
   int ew_blocks_per_sm = 32;
@@ -64,6 +66,7 @@ struct State {
   int gemm_path = 0;  // 0 = auto, 1 = force SIMT, 2 = force tensor-core
   int gemm_bn = 0;    // 0 = auto, else forced tile width (32/64/128/256)
   int use_pdl = 1;    // programmatic dependent launch inside the LSTM time loops
+  int sm_share = 1;   // split-K plans for sm_count / sm_share SMs (two streams sharing the GPU)
   bool pdl_now = false;  // set while a time loop is issuing its kernels
   // graph recording (b200_graph_begin .. b200_graph_end)
   bool capturing = false;

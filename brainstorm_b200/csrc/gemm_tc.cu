@@ -528,8 +528,10 @@ struct TcHost {
   EncodeTiledFn encode = nullptr;
   int* error_flag_host = nullptr;   // mapped pinned memory
   int* error_flag_dev = nullptr;
-  float* partial = nullptr;         // split-K partial tiles (stream-ordered allocation)
-  size_t partial_bytes = 0;
+  // split-K partial tiles (stream-ordered allocation), one buffer per compute stream:
+  // GEMMs of the two streams may run at the same time
+  float* partial[2] = {nullptr, nullptr};
+  size_t partial_bytes[2] = {0, 0};
   std::mutex mu;
   struct Key {
     const void* p; int64_t inner, outer, ld; int box_outer; int mn_major;
@@ -676,8 +678,9 @@ static int gemm_tc_impl(int transa, int transb, int64_t M, int64_t N, int64_t K,
   // kernel adds the partials in a fixed order.
   const int total_kb = (int)ceil_div(K, TC_BK);
   int splits = 1, kb_per_split = total_kb;
-  if (tiles * 2 <= s.sm_count && total_kb >= 2 * TC_CHUNK_KB) {
-    int want = (int)(s.sm_count / tiles);
+  const int64_t sms = s.sm_count / s.sm_share;
+  if (tiles * 2 <= sms && total_kb >= 2 * TC_CHUNK_KB) {
+    int want = (int)(sms / tiles);
     kb_per_split = (int)ceil_div(total_kb, want);
     kb_per_split = (int)ceil_div(kb_per_split, TC_CHUNK_KB) * TC_CHUNK_KB;
     splits = (int)ceil_div(total_kb, kb_per_split);
@@ -690,17 +693,18 @@ static int gemm_tc_impl(int transa, int transb, int64_t M, int64_t N, int64_t K,
     split_stride = M * dst_ld;
     const size_t need = (size_t)splits * split_stride * sizeof(float);
     TcHost& h = tc_host();
-    if (h.partial_bytes < need) {
+    const int si = s.stream_index;
+    if (h.partial_bytes[si] < need) {
       // the buffer outlives the call, so it must not become an allocation of a recorded graph
       B200_REQUIRE(!s.capturing, "the split-K work buffer would have to grow while a graph is being recorded: "
                                  "run the step once before recording it");
-      if (h.partial) B200_CUDA(cudaFreeAsync(h.partial, s.stream));
-      h.partial = nullptr;
-      h.partial_bytes = 0;
-      B200_CUDA(cudaMallocAsync((void**)&h.partial, need, s.stream));
-      h.partial_bytes = need;
+      if (h.partial[si]) B200_CUDA(cudaFreeAsync(h.partial[si], s.stream));
+      h.partial[si] = nullptr;
+      h.partial_bytes[si] = 0;
+      B200_CUDA(cudaMallocAsync((void**)&h.partial[si], need, s.stream));
+      h.partial_bytes[si] = need;
     }
-    dst = h.partial;
+    dst = h.partial[si];
     acc_flag = 0;
   }
   CUtensorMap ma, mb;

@@ -206,17 +206,22 @@ using namespace b200;
 // lays them out (lstm_layer.py:35-67).  xproj is (T*B, 4H) and already holds the
 // input projections x.[Wz;Wi;Wf;Wo]^T; r_stack is [Rz;Ri;Rf;Ro] (4H, H); y_work is a
 // 16-byte aligned (T+1, B, H) array whose slot T the caller has loaded with y[T].
-B200_API int b200_lstm_forward(const float* xproj, const float* r_stack, const float* bias,
-                               const float* peep, float* za, float* zb, float* ia, float* ib, float* fa,
-                               float* fb, float* oa, float* ob, float* ca, float* cb, float* y,
-                               float* y_work, float* r_work, int T, int B, int H, int act) {
+//
+// b200_lstm_forward_steps runs timesteps [t0, t1) only: a caller that overlaps this
+// layer with the layer that produces its input walks the sequence in pieces.
+B200_API int b200_lstm_forward_steps(const float* xproj, const float* r_stack, const float* bias,
+                                     const float* peep, float* za, float* zb, float* ia, float* ib, float* fa,
+                                     float* fb, float* oa, float* ob, float* ca, float* cb, float* y,
+                                     float* y_work, float* r_work, int T, int B, int H, int act, int t0,
+                                     int t1) {
   if (int rc = require_ready()) return rc;
   B200_REQUIRE(T >= 0 && B > 0 && H > 0 && act >= 0 && act <= 4, "bad extents or activation code");
+  B200_REQUIRE(0 <= t0 && t0 <= t1 && t1 <= T, "timestep range [%d, %d) outside [0, %d)", t0, t1, T);
   const State& s = state();
   const int64_t bh = (int64_t)B * H;
   const unsigned grid = (unsigned)ceil_div(bh, 256);
   PdlScope pdl_scope(s.use_pdl != 0);
-  for (int t = 0; t < T; ++t) {
+  for (int t = t0; t < t1; ++t) {
     const int tp = (t + T) % (T + 1);  // t - 1, wrapping to the context slot
     LstmFwdStep p;
     if (int rc = gemm_tc_partials(0, 1, B, 4 * (int64_t)H, H, y_work + tp * bh, H, r_stack, H, r_work,
@@ -235,23 +240,34 @@ B200_API int b200_lstm_forward(const float* xproj, const float* r_stack, const f
   return B200_OK;
 }
 
+B200_API int b200_lstm_forward(const float* xproj, const float* r_stack, const float* bias,
+                               const float* peep, float* za, float* zb, float* ia, float* ib, float* fa,
+                               float* fb, float* oa, float* ob, float* ca, float* cb, float* y,
+                               float* y_work, float* r_work, int T, int B, int H, int act) {
+  return b200_lstm_forward_steps(xproj, r_stack, bias, peep, za, zb, ia, ib, fa, fb, oa, ob, ca, cb, y, y_work,
+                                 r_work, T, B, H, act, 0, T);
+}
+
 // Backward pass over a whole sequence (lstm_layer.py:171-205).  deltas is the
 // (T+1, B, H) output-delta buffer; the ten backward buffers are (T+1, B, H) with zeros
 // in slot T; dg_work is a 16-byte aligned (T+1, B, 4H) array whose slot T is zero: on
 // return slots 0..T-1 hold [dZa, dIa, dFa, dOa] side by side for the weight-gradient
-// and input-delta GEMMs that follow.
-B200_API int b200_lstm_backward(const float* deltas, const float* r_stack, const float* peep,
-                                const float* zb, const float* ib, const float* fb, const float* ob,
-                                const float* ca, const float* cb, float* dza, float* dzb, float* dia,
-                                float* dib, float* dfa, float* dfb, float* doa, float* dob, float* dca,
-                                float* dcb, float* dg_work, float* r_work, int T, int B, int H, int act) {
+// and input-delta GEMMs that follow.  b200_lstm_backward_steps walks timesteps
+// t1-1 down to t0 only (the pieces must be run from the end of the sequence backwards).
+B200_API int b200_lstm_backward_steps(const float* deltas, const float* r_stack, const float* peep,
+                                      const float* zb, const float* ib, const float* fb, const float* ob,
+                                      const float* ca, const float* cb, float* dza, float* dzb, float* dia,
+                                      float* dib, float* dfa, float* dfb, float* doa, float* dob, float* dca,
+                                      float* dcb, float* dg_work, float* r_work, int T, int B, int H, int act,
+                                      int t0, int t1) {
   if (int rc = require_ready()) return rc;
   B200_REQUIRE(T >= 0 && B > 0 && H > 0 && act >= 0 && act <= 4, "bad extents or activation code");
+  B200_REQUIRE(0 <= t0 && t0 <= t1 && t1 <= T, "timestep range [%d, %d) outside [0, %d)", t0, t1, T);
   const State& s = state();
   const int64_t bh = (int64_t)B * H;
   const unsigned grid = (unsigned)ceil_div(bh, 256);
   PdlScope pdl_scope(s.use_pdl != 0);
-  for (int t = T - 1; t >= 0; --t) {
+  for (int t = t1 - 1; t >= t0; --t) {
     const int tp = (t + T) % (T + 1), tn = t + 1;
     LstmBwdStep p;
     p.rpart = nullptr; p.splits = 0; p.split_stride = 0; p.rld = 0;
@@ -273,4 +289,13 @@ B200_API int b200_lstm_backward(const float* deltas, const float* r_stack, const
     B200_LAUNCH_CHECK();
   }
   return B200_OK;
+}
+
+B200_API int b200_lstm_backward(const float* deltas, const float* r_stack, const float* peep,
+                                const float* zb, const float* ib, const float* fb, const float* ob,
+                                const float* ca, const float* cb, float* dza, float* dzb, float* dia,
+                                float* dib, float* dfa, float* dfb, float* doa, float* dob, float* dca,
+                                float* dcb, float* dg_work, float* r_work, int T, int B, int H, int act) {
+  return b200_lstm_backward_steps(deltas, r_stack, peep, zb, ib, fb, ob, ca, cb, dza, dzb, dia, dib, dfa, dfb, doa,
+                                  dob, dca, dcb, dg_work, r_work, T, B, H, act, 0, T);
 }

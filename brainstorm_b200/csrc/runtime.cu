@@ -81,6 +81,8 @@ B200_API int b200_init(int device) {
                prop.major, prop.minor);
   s.sm_count = prop.multiProcessorCount;
   B200_CUDA(cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking));
+  s.streams[0] = s.stream;
+  s.stream_index = 0;
   cudaMemPool_t pool;
   B200_CUDA(cudaDeviceGetDefaultMemPool(&pool, device));
   uint64_t keep = UINT64_MAX;
@@ -110,6 +112,7 @@ B200_API int b200_set_tuning(int key, int value) {
     case 2: B200_REQUIRE(value >= 0 && value <= 2, "gemm path must be 0, 1 or 2"); s.gemm_path = value; break;
     case 3: s.gemm_bn = value; break;
     case 5: s.use_pdl = value ? 1 : 0; break;
+    case 6: B200_REQUIRE(value >= 1 && value <= 8, "SM share divisor out of range"); s.sm_share = value; break;
     default: return set_error(B200_ERR_ARG, "unknown tuning key %d", key);
   }
   return B200_OK;
@@ -117,7 +120,48 @@ B200_API int b200_set_tuning(int key, int value) {
 
 B200_API uint64_t b200_launch_count(void) { return state().launches; }
 
-B200_API uint64_t b200_stream(void) { return (uint64_t)(uintptr_t)state().stream; }
+B200_API uint64_t b200_stream(void) { return (uint64_t)(uintptr_t)state().streams[0]; }
+
+// ---- a second compute stream ---------------------------------------------------------
+// Work of two layers that does not depend on each other timestep by timestep (a stack
+// of LSTM layers: layer l+1 at time t needs layer l only up to time t) can run side by
+// side.  b200_use_stream(1) makes every following call of this library queue its work
+// on the side stream, b200_use_stream(0) returns to the main stream.  Ordering
+// between the two is explicit: b200_mark records a marker on the current stream,
+// b200_wait_mark makes the current stream wait for one.  Allocations are
+// stream-ordered: memory that the side stream touches before it has waited for the
+// main stream must be allocated while the side stream is current.
+B200_API int b200_use_stream(int index) {
+  if (int rc = require_ready()) return rc;
+  State& s = state();
+  B200_REQUIRE(index == 0 || index == 1, "stream index must be 0 or 1");
+  if (!s.streams[index]) B200_CUDA(cudaStreamCreateWithFlags(&s.streams[index], cudaStreamNonBlocking));
+  s.stream_index = index;
+  s.stream = s.streams[index];
+  return B200_OK;
+}
+
+B200_API int b200_mark_create(uint64_t* mark) {
+  B200_REQUIRE(mark != nullptr, "mark is NULL");
+  cudaEvent_t e;
+  B200_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  *mark = (uint64_t)(uintptr_t)e;
+  return B200_OK;
+}
+B200_API int b200_mark(uint64_t mark) {
+  if (int rc = require_ready()) return rc;
+  B200_CUDA(cudaEventRecord((cudaEvent_t)(uintptr_t)mark, state().stream));
+  return B200_OK;
+}
+B200_API int b200_wait_mark(uint64_t mark) {
+  if (int rc = require_ready()) return rc;
+  B200_CUDA(cudaStreamWaitEvent(state().stream, (cudaEvent_t)(uintptr_t)mark, 0));
+  return B200_OK;
+}
+B200_API int b200_mark_destroy(uint64_t mark) {
+  if (mark) B200_CUDA(cudaEventDestroy((cudaEvent_t)(uintptr_t)mark));
+  return B200_OK;
+}
 
 B200_API int b200_malloc(uint64_t* ptr, uint64_t bytes, int zero) {
   if (int rc = require_ready()) return rc;
@@ -166,6 +210,7 @@ B200_API int b200_graph_begin(void) {
   if (int rc = require_ready()) return rc;
   State& s = state();
   B200_REQUIRE(!s.capturing, "a graph is already being recorded");
+  B200_REQUIRE(s.stream_index == 0, "a recording starts on the main stream");
   if (!g_rec.side_stream) B200_CUDA(cudaStreamCreateWithFlags(&g_rec.side_stream, cudaStreamNonBlocking));
   if (!s.replay_epoch) {
     B200_CUDA(cudaMalloc((void**)&s.replay_epoch, sizeof(uint64_t)));

@@ -15,8 +15,19 @@ runs, per timestep, one stacked recurrent GEMM and one gate kernel
 Every buffer the reference layer fills is filled with the same values (to
 rounding: the recurrent contributions of the four gates are summed inside one
 GEMM instead of one after the other).
+
+Stacked LSTM layers run side by side.  The reference walks a network layer by
+layer (brainstorm/structure/network.py:429-430, :441-444), but layer l+1 at time t
+needs layer l only up to time t, and a timestep is latency-bound (it leaves most
+of the GPU idle).  A fused layer therefore marks the stream after every piece of
+``PIECE`` timesteps; a fused layer called directly after the layer that produced
+its input (forward) or its output deltas (backward) walks the same pieces on the
+library's second stream, each piece as soon as the other layer has finished it,
+and the main stream joins it before the call returns.
 """
 from __future__ import annotations
+
+import ctypes
 
 from brainstorm.layers.lstm_layer import LstmLayerImpl
 from brainstorm.utils import flatten_time, flatten_time_and_features
@@ -26,6 +37,34 @@ from .array import B200Array
 from .handler import B200Handler
 
 _ACT = {'sigmoid': 0, 'tanh': 1, 'rel': 2, 'el': 3, 'linear': 4}
+
+PIECE = 20            # timesteps per piece when stacked layers overlap (0 = never overlap)
+_forward_done = {}    # output address -> _Pieces of the fused layer that has just filled it
+_backward_done = {}   # input-delta address -> _Pieces of the fused layer that has just filled it
+
+
+class _Pieces(object):
+    """What a fused layer leaves behind for the fused layer that is called next."""
+
+    def __init__(self, ranges, marks, start, stream, launches, y_work=None):
+        self.ranges = ranges        # [(t0, t1), ...] in the order they were run
+        self.marks = marks          # marks[i] is reached when piece i is complete
+        self.start = start          # mark on the producer's stream from before its first piece
+        self.stream = stream        # 0 = main, 1 = side
+        self.launches = launches    # library launch counter when the producer returned
+        self.y_work = y_work        # forward: aligned copy of the output sequence
+
+
+def _ranges(T):
+    if PIECE <= 0 or T < 2 * PIECE:
+        return [(0, T)]
+    return [(t, min(t + PIECE, T)) for t in range(0, T, PIECE)]
+
+
+def _new_mark():
+    m = ctypes.c_uint64()
+    check(lib.b200_mark_create(ctypes.byref(m)))
+    return m.value
 
 
 def _stack(views, shape):
@@ -53,44 +92,88 @@ class FusedLstmLayerImpl(LstmLayerImpl):
         return (_stack([Wz, Wi, Wf, Wo], (4 * H, in_size)), _stack([Rz, Ri, Rf, Ro], (4 * H, H)),
                 _stack([bz, bi, bf, bo], (4 * H,)), _stack([pi, pf, po], (3 * H,)))
 
+    def _marks(self, n):
+        marks = self.__dict__.setdefault('_mark_pool', [])
+        while len(marks) < n + 2:
+            marks.append(_new_mark())
+        return marks[2:n + 2], marks[0], marks[1]      # piece marks, start mark, done mark
+
     def forward_pass(self, buffers, training_pass=True):
         h = self.handler
         x = buffers.inputs.default
         y = buffers.outputs.default
         T, B = x.shape[0], x.shape[1]
         H = self.size
+        _forward_done.pop(y.ptr, None)
+        self._fused = None
         flat_x = flatten_time_and_features(x)
         stacks = self._stacks(buffers.parameters, flat_x.shape[1])
         hubs = list(buffers.internals)[:10] + [y]
         if (not isinstance(h, B200Handler) or any(s is None for s in stacks) or
                 not all(a.is_contiguous for a in hubs) or T == 0):
-            self._fused = None
             return LstmLayerImpl.forward_pass(self, buffers, training_pass)
         Wst, Rst, bst, pst = stacks
         (Za, Zb, Ia, Ib, Fa, Fb, Oa, Ob, Ca, Cb) = hubs[:10]
-        xproj = B200Array.empty((T * B, 4 * H), zero=False)
-        h.dot_mm(flat_x, Wst, xproj, transb=True)               # lstm_layer.py:110-113, stacked
-        Rw = _aligned(h, Rst)
-        y_work = B200Array.empty((T + 1, B, H), zero=False)
-        h.copy_to(y[T], y_work[T])                              # context: y[t-1] at t = 0
-        r_work = B200Array.empty((B, 4 * H), zero=False)
-        check(lib.b200_lstm_forward(xproj.ptr, Rw.ptr, bst.ptr, pst.ptr, Za.ptr, Zb.ptr, Ia.ptr, Ib.ptr,
-                                    Fa.ptr, Fb.ptr, Oa.ptr, Ob.ptr, Ca.ptr, Cb.ptr, y.ptr, y_work.ptr,
-                                    r_work.ptr, T, B, H, _ACT[self.activation]))
-        self._fused = (Rw, y_work, r_work)
+        ranges = _ranges(T)
+        marks, start, done = self._marks(len(ranges))
+        # the layer that has just produced x, if it left pieces to follow
+        prod = _forward_done.pop(x.ptr, None)
+        if prod is not None and not (prod.ranges == ranges and len(ranges) > 1 and prod.stream == 0 and
+                                     prod.y_work.shape == (T + 1,) + tuple(x.shape[1:]) and
+                                     prod.launches == lib.b200_launch_count()):
+            prod = None
+        stream = 0 if prod is None else 1
+        if stream:
+            check(lib.b200_use_stream(1))
+        try:
+            if stream:
+                check(lib.b200_wait_mark(prod.start))       # everything queued before the producer's pieces
+            else:
+                check(lib.b200_mark(start))
+            xproj = B200Array.empty((T * B, 4 * H), zero=False)
+            Rw = _aligned(h, Rst)
+            y_work = B200Array.empty((T + 1, B, H), zero=False)
+            h.copy_to(y[T], y_work[T])                          # context: y[t-1] at t = 0
+            r_work = B200Array.empty((B, 4 * H), zero=False)
+            if prod is None:
+                h.dot_mm(flat_x, Wst, xproj, transb=True)       # lstm_layer.py:110-113, stacked
+            else:
+                Ww = _aligned(h, Wst)
+                src = flatten_time_and_features(prod.y_work[:T])   # the same values as x, 16-byte aligned
+            for i, (t0, t1) in enumerate(ranges):
+                if prod is not None:
+                    check(lib.b200_wait_mark(prod.marks[i]))
+                    h.dot_mm(src[t0 * B:t1 * B], Ww, xproj[t0 * B:t1 * B], transb=True)
+                check(lib.b200_lstm_forward_steps(xproj.ptr, Rw.ptr, bst.ptr, pst.ptr, Za.ptr, Zb.ptr, Ia.ptr,
+                                                  Ib.ptr, Fa.ptr, Fb.ptr, Oa.ptr, Ob.ptr, Ca.ptr, Cb.ptr, y.ptr,
+                                                  y_work.ptr, r_work.ptr, T, B, H, _ACT[self.activation], t0, t1))
+                if len(ranges) > 1:
+                    check(lib.b200_mark(marks[i]))
+            if stream:
+                check(lib.b200_mark(done))
+        finally:
+            if stream:
+                check(lib.b200_use_stream(0))
+        if stream:
+            check(lib.b200_wait_mark(done))                     # the main stream joins
+        self._fused = (Rw, y_work, r_work, prod is not None, prod.y_work if prod is not None else None)
+        if len(ranges) > 1:
+            _forward_done[y.ptr] = _Pieces(ranges, marks, start if not stream else done, stream,
+                                           lib.b200_launch_count(), y_work)
 
     def backward_pass(self, buffers):
         fused = getattr(self, '_fused', None)
+        dx = buffers.input_deltas.default
+        _backward_done.pop(dx.ptr, None)
         if fused is None:
             return LstmLayerImpl.backward_pass(self, buffers)
         h = self.handler
-        Rw, y_work, r_work = fused
+        Rw, y_work, r_work, fed_by_lstm, x_work = fused
         x = buffers.inputs.default
-        dx = buffers.input_deltas.default
         deltas = buffers.output_deltas.default
         T, B = x.shape[0], x.shape[1]
         H = self.size
-        flat_x = flatten_time_and_features(x)
+        flat_x = flatten_time_and_features(x) if x_work is None else flatten_time_and_features(x_work[:T])
         Wst, _, _, pst = self._stacks(buffers.parameters, flat_x.shape[1])
         dWst, dRst, dbst, _ = self._stacks(buffers.gradients, flat_x.shape[1])
         (dpi, dpf, dpo) = list(buffers.gradients)[4:7]
@@ -99,16 +182,50 @@ class FusedLstmLayerImpl(LstmLayerImpl):
         if dWst is None or dRst is None or dbst is None or not deltas.is_contiguous:
             return LstmLayerImpl.backward_pass(self, buffers)
 
-        dG = B200Array.empty((T + 1, B, 4 * H), zero=False)
-        h.fill(dG[T], 0.0)
-        h.fill(dCa, 0.0)                                        # lstm_layer.py:168
-        check(lib.b200_lstm_backward(deltas.ptr, Rw.ptr, pst.ptr, Zb.ptr, Ib.ptr, Fb.ptr, Ob.ptr, Ca.ptr,
-                                     Cb.ptr, dZa.ptr, dZb.ptr, dIa.ptr, dIb.ptr, dFa.ptr, dFb.ptr,
-                                     dOa.ptr, dOb.ptr, dCa.ptr, dCb.ptr, dG.ptr, r_work.ptr, T, B, H,
-                                     _ACT[self.activation]))
+        ranges = _ranges(T)[::-1]                               # from the end of the sequence backwards
+        marks, start, done = self._marks(len(ranges))
+        flat_dx = flatten_time_and_features(dx)
+        # the layer that has just added its input deltas to `deltas`, if it left pieces to follow
+        prod = _backward_done.pop(deltas.ptr, None)
+        if prod is not None and not (prod.ranges == ranges and len(ranges) > 1 and prod.stream == 0 and
+                                     prod.launches == lib.b200_launch_count()):
+            prod = None
+        # a layer fed by a fused LSTM layer hands its input deltas over piece by piece
+        by_piece = fed_by_lstm and len(ranges) > 1
+        stream = 0 if prod is None else 1
+        if stream:
+            check(lib.b200_use_stream(1))
+        try:
+            if stream:
+                check(lib.b200_wait_mark(prod.start))
+            else:
+                check(lib.b200_mark(start))
+            dG = B200Array.empty((T + 1, B, 4 * H), zero=False)
+            h.fill(dG[T], 0.0)
+            h.fill(dCa, 0.0)                                    # lstm_layer.py:168
+            Ww = _aligned(h, Wst) if by_piece else Wst
+            for i, (t0, t1) in enumerate(ranges):
+                if prod is not None:
+                    check(lib.b200_wait_mark(prod.marks[i]))
+                check(lib.b200_lstm_backward_steps(deltas.ptr, Rw.ptr, pst.ptr, Zb.ptr, Ib.ptr, Fb.ptr, Ob.ptr,
+                                                   Ca.ptr, Cb.ptr, dZa.ptr, dZb.ptr, dIa.ptr, dIb.ptr, dFa.ptr,
+                                                   dFb.ptr, dOa.ptr, dOb.ptr, dCa.ptr, dCb.ptr, dG.ptr,
+                                                   r_work.ptr, T, B, H, _ACT[self.activation], t0, t1))
+                if by_piece:                                    # input deltas of this piece (:216-219)
+                    h.dot_add_mm(dG[t0:t1].reshape(((t1 - t0) * B, 4 * H)), Ww, flat_dx[t0 * B:t1 * B])
+                    check(lib.b200_mark(marks[i]))
+            if stream:
+                check(lib.b200_mark(done))
+        finally:
+            if stream:
+                check(lib.b200_use_stream(0))
+        if stream:
+            check(lib.b200_wait_mark(done))                     # the main stream joins
+        handed_over = _Pieces(ranges, marks, start if not stream else done, stream, 0) if by_piece else None
         dGf = dG[:T].reshape((T * B, 4 * H))
         # input deltas and input-weight gradients (:216-224), four gates at once
-        h.dot_add_mm(dGf, Wst, flatten_time_and_features(dx))
+        if not by_piece:
+            h.dot_add_mm(dGf, Wst, flat_dx)
         h.dot_add_mm(dGf, flat_x, dWst, transa=True)
         # biases (:226-234)
         tmp = B200Array.empty((4 * H,), zero=False)
@@ -121,21 +238,24 @@ class FusedLstmLayerImpl(LstmLayerImpl):
                          y_work[:T - 1].reshape(((T - 1) * B, H)), dRst, transa=True)
         # peepholes (:236-278)
         dWc = B200Array.empty(dpo.shape, zero=False)
-        prod = B200Array.empty((T * B, H), zero=False)
-        h.mult_tt(flatten_time(Ca[:T]), flatten_time(dOa[:T]), prod)
-        h.sum_t(prod, axis=0, out=dWc)
+        products = B200Array.empty((T * B, H), zero=False)
+        h.mult_tt(flatten_time(Ca[:T]), flatten_time(dOa[:T]), products)
+        h.sum_t(products, axis=0, out=dWc)
         h.add_tt(dpo, dWc, dpo)
         for d_gate, d_peep in ((dIa, dpi), (dFa, dpf)):
             if T > 1:
-                p1 = prod[:(T - 1) * B]
+                p1 = products[:(T - 1) * B]
                 h.mult_tt(flatten_time(Ca[:T - 1]), flatten_time(d_gate[1:T]), p1)
                 h.sum_t(p1, axis=0, out=dWc)
                 h.add_tt(d_peep, dWc, d_peep)
-            p0 = prod[:B]
+            p0 = products[:B]
             h.mult_tt(dCa[T], dIa[0], p0)                        # :273-278 (both use dIa[0])
             h.sum_t(p0, axis=0, out=dWc)
             h.add_tt(d_peep, dWc, d_peep)
         self._fused = None
+        if handed_over is not None:
+            handed_over.launches = lib.b200_launch_count()
+            _backward_done[dx.ptr] = handed_over
 
 
 def fuse_lstm_layers(net):

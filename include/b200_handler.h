@@ -35,9 +35,25 @@ int b200_device_count(int* count);
 int b200_init(int device);
 int b200_device_info(int* device, int* sm_count, uint64_t* free_bytes, uint64_t* total_bytes);
 /* key 0: elementwise blocks per SM; 1: elementwise threads per block;
- * 2: GEMM path (0 auto, 1 CUDA cores, 2 tensor cores only). */
+ * 2: GEMM path (0 auto, 1 CUDA cores, 2 tensor cores only); 3: forced GEMM tile width;
+ * 5: programmatic dependent launch inside the LSTM time loops (default 1);
+ * 6: split-K plans for 1/value of the SMs (default 1; 2 while two streams share the GPU). */
 int b200_set_tuning(int key, int value);
-uint64_t b200_stream(void);
+uint64_t b200_stream(void);                            /* the main stream (a cudaStream_t) */
+/* A second compute stream, for work that may run beside the main stream's (a stack of
+ * LSTM layers: the reference walks layer by layer, brainstorm/structure/network.py:429-430,
+ * but layer l+1 at time t needs layer l only up to time t).  b200_use_stream(1) makes
+ * every following call queue on the side stream, b200_use_stream(0) returns to the
+ * main stream.  Ordering between the streams is explicit: b200_mark records a marker
+ * on the current stream, b200_wait_mark makes the current stream wait for one.  Memory
+ * that the side stream touches before it has waited for the main stream must have been
+ * allocated while the side stream was current (allocations are stream-ordered).  The
+ * reference has no counterpart. */
+int b200_use_stream(int index);
+int b200_mark_create(uint64_t* mark);
+int b200_mark(uint64_t mark);
+int b200_wait_mark(uint64_t mark);
+int b200_mark_destroy(uint64_t mark);
 /* Number of kernels this library has launched in this process so far. */
 uint64_t b200_launch_count(void);
 int b200_sync(void);                                   /* synchronises */
@@ -211,6 +227,19 @@ int b200_lstm_backward(const float* deltas, const float* r_stack, const float* p
                        const float* zb, const float* ib, const float* fb, const float* ob, const float* ca, const float* cb,
                        float* dza, float* dzb, float* dia, float* dib, float* dfa, float* dfb, float* doa, float* dob,
                        float* dca, float* dcb, float* dg_work, float* r_work, int T, int B, int H, int act);
+/* The same passes over a piece of the sequence: forward timesteps t0 .. t1-1, backward
+ * t1-1 down to t0 (pieces in that order).  For callers that run a stack of LSTM layers
+ * side by side (see b200_use_stream): layer l+1 can start a piece as soon as layer l
+ * has finished it. */
+int b200_lstm_forward_steps(const float* xproj, const float* r_stack, const float* bias, const float* peep,
+                            float* za, float* zb, float* ia, float* ib, float* fa, float* fb, float* oa, float* ob,
+                            float* ca, float* cb, float* y, float* y_work, float* r_work, int T, int B, int H, int act,
+                            int t0, int t1);
+int b200_lstm_backward_steps(const float* deltas, const float* r_stack, const float* peep,
+                             const float* zb, const float* ib, const float* fb, const float* ob, const float* ca, const float* cb,
+                             float* dza, float* dzb, float* dia, float* dib, float* dfa, float* dfb, float* doa, float* dob,
+                             float* dca, float* dcb, float* dg_work, float* r_work, int T, int B, int H, int act,
+                             int t0, int t1);
 
 /* ---- convolution and pooling (NHWC): conv2d_forward_batch :411, conv2d_backward_batch :392,
  *      maxpool2d_* :590/:572, avgpool2d_* :314/:297; numpy_handler.py:149,110,216,210,94,89 with

@@ -18,7 +18,7 @@ def _pair(builder, fused=False, **kw):
     net_gpu.set_handler(B200Handler(seed=77, rng_mode='host'))
     if fused:
         from brainstorm_b200.fused_lstm import fuse_lstm_layers
-        assert len(fuse_lstm_layers(net_gpu)) == 2
+        assert len(fuse_lstm_layers(net_gpu)) == kw.get('layers', 2)
     p_cpu = net_cpu.get('parameters')
     p_gpu = net_gpu.get('parameters')
     assert np.array_equal(p_cpu, p_gpu)
@@ -100,6 +100,38 @@ def test_fused_lstm_layer_matches_reference_layer(shape):
                 path = '%s.%s.%s' % (lname, kind, bname)
                 c, g = net_cpu.get(path), net_gpu.get(path)
                 if c.shape[0] == T + 1:    # the context slot is not part of the pass
+                    c, g = c[:T], g[:T]
+                _close(g, c, 2e-4, path)
+
+
+@pytest.mark.parametrize('piece,shape', [(2, dict(time=7, batch=9, vocab=23, hidden=32)),
+                                         (3, dict(time=12, batch=128, vocab=205, hidden=200)),
+                                         (2, dict(time=6, batch=64, vocab=48, hidden=128, layers=3))],
+                         ids=['ragged', 'wide', 'three-layers'])
+def test_stacked_fused_lstm_layers_side_by_side(piece, shape, monkeypatch):
+    """With pieces shorter than the sequence the second LSTM layer runs on the second
+    stream, piece by piece behind the first one (forward) and ahead of it (backward).
+    Same checks as above, and the overlap must really have been taken."""
+    from brainstorm_b200 import fused_lstm, workloads
+    from brainstorm_b200._lib import lib
+    monkeypatch.setattr(fused_lstm, 'PIECE', piece)
+    used = []
+    real = lib.b200_use_stream
+    monkeypatch.setattr(lib, 'b200_use_stream', lambda i: (used.append(i), real(i))[1])
+    net_cpu, net_gpu = _check_training(workloads.lstm, steps=2, rtol=2e-4, fused=True, **shape)
+    assert used.count(1) >= 2 * 3            # forward and backward of (at least) three passes
+    for net in (net_cpu, net_gpu):
+        net.forward_pass(training_pass=True)
+        net.backward_pass()
+    T = shape['time']
+    for lname in net_cpu.layers:
+        if not lname.startswith('Lstm'):
+            continue
+        for kind in ('internals', 'outputs', 'input_deltas'):
+            for bname in net_cpu.buffer[lname][kind].keys():
+                path = '%s.%s.%s' % (lname, kind, bname)
+                c, g = net_cpu.get(path), net_gpu.get(path)
+                if c.shape[0] == T + 1:
                     c, g = c[:T], g[:T]
                 _close(g, c, 2e-4, path)
 
