@@ -424,6 +424,8 @@ def run_b200(args):
         if rank == 0:
             print(json.dumps({'metric': 'lstm_train_sequences_per_s', 'value': lstm.get('sequences_per_s'),
                               'unit': 'sequences/s', 'n_gpus': world, 'lstm': lstm}))
+        if world > 1:
+            dist.destroy_process_group()
         return
     ROWS = args.rows
     # ---- operands: page-locked host copies (for e2e) and device-resident arrays

@@ -192,6 +192,21 @@ def test_graphed_stepper_trains_the_lstm_bit_for_bit_like_the_plain_stepper(fuse
 
 @pytest.mark.gpu
 @needs_reference
+def test_recording_a_step_whose_lstm_layers_run_on_two_streams(monkeypatch):
+    """The second LSTM layer of a stack runs on the library's side stream; a recording
+    has to follow the fork and the join."""
+    from brainstorm_b200 import GraphedStepper, fused_lstm, workloads
+    monkeypatch.setattr(fused_lstm, 'PIECE', 2)
+    kw = dict(time=6, batch=64, vocab=48, hidden=128)
+    p_plain, l_plain, _ = _train(workloads.lstm, lambda s: s, 5, fused=True, **kw)
+    p_graph, l_graph, st = _train(workloads.lstm, GraphedStepper, 5, fused=True, **kw)
+    assert st._step is not None
+    assert l_plain == l_graph
+    assert np.array_equal(p_plain, p_graph)
+
+
+@pytest.mark.gpu
+@needs_reference
 def test_graphed_stepper_records_again_when_a_frozen_scalar_or_the_batch_shape_changes():
     import brainstorm as bs
     from brainstorm_b200 import B200Handler, GraphedStepper, workloads
