@@ -39,8 +39,16 @@ from .handler import B200Handler
 _ACT = {'sigmoid': 0, 'tanh': 1, 'rel': 2, 'el': 3, 'linear': 4}
 
 PIECE = 32            # about this many timesteps per piece when stacked layers overlap (0 = never overlap)
-_forward_done = {}    # output address -> _Pieces of the fused layer that has just filled it
-_backward_done = {}   # input-delta address -> _Pieces of the fused layer that has just filled it
+# What the fused layer that ran last left behind, per direction: (address of the array it
+# filled, _Pieces).  Only the layer called directly afterwards may take it, so one slot each.
+_handover = {'forward': None, 'backward': None}
+
+
+def _take(direction, address):
+    """The pieces left for the array at `address`, if the last fused layer left any; the
+    slot is emptied either way."""
+    left, _handover[direction] = _handover[direction], None
+    return left[1] if left is not None and left[0] == address else None
 
 
 class _Pieces(object):
@@ -119,8 +127,8 @@ class FusedLstmLayerImpl(LstmLayerImpl):
         y = buffers.outputs.default
         T, B = x.shape[0], x.shape[1]
         H = self.size
-        _forward_done.pop(y.ptr, None)
         self._fused = None
+        prod = _take('forward', x.ptr)      # the layer that has just produced x, if it left pieces to follow
         flat_x = flatten_time_and_features(x)
         stacks = self._stacks(buffers.parameters, flat_x.shape[1])
         hubs = list(buffers.internals)[:10] + [y]
@@ -131,8 +139,6 @@ class FusedLstmLayerImpl(LstmLayerImpl):
         (Za, Zb, Ia, Ib, Fa, Fb, Oa, Ob, Ca, Cb) = hubs[:10]
         ranges = _ranges(T)
         marks, start, done = self._marks(len(ranges))
-        # the layer that has just produced x, if it left pieces to follow
-        prod = _forward_done.pop(x.ptr, None)
         if prod is not None and not (prod.ranges == ranges and len(ranges) > 1 and prod.stream == 0 and
                                      prod.y_work.shape == (T + 1,) + tuple(x.shape[1:]) and
                                      prod.launches == lib.b200_launch_count()):
@@ -180,19 +186,20 @@ class FusedLstmLayerImpl(LstmLayerImpl):
             check(lib.b200_wait_mark(done))                     # the main stream joins
         self._fused = (Rw, y_work, r_work, prod is not None, prod.y_work if prod is not None else None)
         if len(ranges) > 1:
-            _forward_done[y.ptr] = _Pieces(self, ranges, marks, start if not stream else done, stream,
-                                           lib.b200_launch_count(), y_work)
+            _handover['forward'] = (y.ptr, _Pieces(self, ranges, marks, start if not stream else done, stream,
+                                                   lib.b200_launch_count(), y_work))
 
     def backward_pass(self, buffers):
         fused = getattr(self, '_fused', None)
         dx = buffers.input_deltas.default
-        _backward_done.pop(dx.ptr, None)
+        deltas = buffers.output_deltas.default
+        # the layer that has just added its input deltas to `deltas`, if it left pieces to follow
+        prod = _take('backward', deltas.ptr)
         if fused is None:
             return LstmLayerImpl.backward_pass(self, buffers)
         h = self.handler
         Rw, y_work, r_work, fed_by_lstm, x_work = fused
         x = buffers.inputs.default
-        deltas = buffers.output_deltas.default
         T, B = x.shape[0], x.shape[1]
         H = self.size
         flat_x = flatten_time_and_features(x) if x_work is None else flatten_time_and_features(x_work[:T])
@@ -207,8 +214,6 @@ class FusedLstmLayerImpl(LstmLayerImpl):
         ranges = _ranges(T)[::-1]                               # from the end of the sequence backwards
         marks, start, done = self._marks(len(ranges))
         flat_dx = flatten_time_and_features(dx)
-        # the layer that has just added its input deltas to `deltas`, if it left pieces to follow
-        prod = _backward_done.pop(deltas.ptr, None)
         if prod is not None and not (prod.ranges == ranges and len(ranges) > 1 and prod.stream == 0 and
                                      prod.launches == lib.b200_launch_count()):
             prod = None
@@ -282,7 +287,7 @@ class FusedLstmLayerImpl(LstmLayerImpl):
         self._fused = None
         if handed_over is not None:
             handed_over.launches = lib.b200_launch_count()
-            _backward_done[dx.ptr] = handed_over
+            _handover['backward'] = (dx.ptr, handed_over)
 
 
 def fuse_lstm_layers(net):
