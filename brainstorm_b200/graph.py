@@ -135,6 +135,8 @@ class GraphedStepper(_StepperBase):
                 type(self.stepper).__name__, _scalars(self.stepper))
 
     def run(self):
+        if getattr(self.net.handler, '_comm', None) is not None:
+            return self.stepper.run()       # data parallel: the collectives are not recorded, run as usual
         key = self._state_key()
         if key != self._key:
             self.invalidate()
