@@ -234,11 +234,58 @@ def cpu_suite_time(rows, cols, seed, threads, steps, warmup):
     return nbytes / dt / 1e9, dt, kind
 
 
+CPU_LSTM_BATCH = 32     # sequences per step of the reference arm's LSTM sample
+
+
+def reference_lstm_step(batch=None, steps=1):
+    """The character-LSTM training step (time 100, 205 symbols, 2 x 1000 units, SGD) on the
+    reference's own stack: NumpyHandler, LstmLayerImpl, SgdStepper, unchanged.  A bounded
+    sample: `batch` sequences per step instead of 128 (a step costs about batch / 16 seconds
+    of host time; numpy's BLAS uses all cores)."""
+    batch = batch or CPU_LSTM_BATCH
+    ref = os.path.join(ROOT, 'baseline', '_ref')
+    if os.path.isdir(os.path.join(ref, 'brainstorm')) and ref not in sys.path:
+        sys.path.insert(0, ref)
+    try:
+        import brainstorm  # noqa: F401
+        from brainstorm.handlers import NumpyHandler
+    except Exception as e:
+        return {'unavailable': 'the reference install (baseline/_ref) is not importable: %s' % e}
+    import importlib.util
+    spec = importlib.util.spec_from_file_location('b200_workloads', os.path.join(ROOT, 'brainstorm_b200', 'workloads.py'))
+    workloads = importlib.util.module_from_spec(spec)    # the network builder only: no GPU library is loaded
+    spec.loader.exec_module(workloads)
+    net, data, stepper = workloads.lstm(time=100, batch=batch)
+    net.set_handler(NumpyHandler(np.float32))
+    st = stepper()
+    st.start(net)
+
+    def step():
+        net.provide_external_data(data)
+        st.run()
+        return float(net.get_loss_values()['total_loss'])
+
+    step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        loss = step()
+    dt = (time.perf_counter() - t0) / steps
+    return {'sequences_per_s': round(batch / dt, 2), 'ms_per_step': round(dt * 1e3, 1), 'time_steps': 100,
+            'batch': batch, 'hidden': 1000, 'layers': 2, 'steps': steps, 'loss': round(loss, 4), 'kind': 'reference',
+            'cores': os.cpu_count() or 1,
+            'sample': '%d sequences per step instead of 128, %d step(s) after 1 warm-up' % (batch, steps)}
+
+
 def run_reference(args):
     rank = int(os.environ.get('RANK', '0'))
     if rank != 0:
         return
     threads = os.cpu_count() or 1
+    if args.only == 'lstm':
+        res = reference_lstm_step()
+        print(json.dumps({'impl': 'reference', 'metric': 'lstm_train_sequences_per_s',
+                          'value': res.get('sequences_per_s'), 'unit': 'sequences/s', 'n_gpus': args.gpus, 'lstm': res}))
+        return
     steps = max(1, min(args.steps, 5))
     gbs, dt, kind = cpu_suite_time(CPU_SAMPLE_ROWS, COLS, SEED, threads, steps, min(args.warmup, 1))
     sample = '%d of %d rows per step (same %d columns, same ops), %d steps' % (
@@ -255,6 +302,8 @@ def run_reference(args):
         'e2e': {'value': round(gbs, 3), 'unit': UNIT, 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
         'gpu_launches': 0,
     }
+    if args.only == 'all':
+        line['lstm'] = reference_lstm_step()
     print(json.dumps(line))
 
 

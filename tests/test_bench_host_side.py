@@ -41,12 +41,14 @@ def test_cpu_leg_reports_throughput():
 def test_reference_arm_prints_one_json_line(monkeypatch):
     env = dict(os.environ, RANK='0')
     code = ("import sys; sys.argv=['bench.py','--impl','reference','--steps','1','--warmup','0'];"
-            "import bench; bench.CPU_SAMPLE_ROWS=128; bench.main()")
+            "import bench; bench.CPU_SAMPLE_ROWS=128; bench.CPU_LSTM_BATCH=2; bench.main()")
     out = subprocess.run([sys.executable, '-c', code], capture_output=True, text=True, cwd=ROOT, env=env)
     assert out.returncode == 0, out.stderr[-2000:]
     line = json.loads(out.stdout.strip().splitlines()[-1])
     assert line['impl'] == 'reference' and line['value'] > 0 and line['unit'] == 'GB/s'
     assert line['cpu_baseline']['cores'] >= 1 and line['e2e']['h2d_bytes_per_step'] == 0
+    # the LSTM half of the metric on the reference's own stack (when its install is present)
+    assert 'unavailable' in line['lstm'] or (line['lstm']['sequences_per_s'] > 0 and line['lstm']['batch'] == 2)
     other = subprocess.run([sys.executable, '-c', code], capture_output=True, text=True, cwd=ROOT,
                            env=dict(env, RANK='1'))
     assert other.returncode == 0 and other.stdout.strip() == ''      # other ranks do no work
