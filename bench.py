@@ -422,6 +422,49 @@ def other_training_configs(H, rank, lib, only=None):
     return out
 
 
+def highway_bn_sharded(H, world, rank, barrier, lib, steps=3):
+    """The Highway + BatchNorm stack with its batch of 8192 sharded over the ranks (strong
+    scaling: 8192 / world rows per GPU): gradients all-reduced per layer, BatchNorm batch
+    statistics completed across the shards inside ``sum_t(axis=0)`` (NCCL, 16 KiB each)."""
+    try:
+        import brainstorm  # noqa: F401
+    except Exception as e:
+        return {'unavailable': 'brainstorm is not importable: %s' % e}
+    import torch
+    import torch.distributed as dist
+    from brainstorm_b200 import workloads
+    from brainstorm_b200.parallel import Comm, data_parallel
+    global_batch = 8192
+    net, data, stepper = workloads.highway_bn(batch=global_batch // world, data_seed=rank)
+    net.set_handler(H)
+    data_parallel(net, Comm(), axis0_reduce='avg')
+    st = stepper()
+    st.start(net)
+
+    def step():
+        net.provide_external_data(data)
+        st.run()
+        return float(net.get_loss_values()['total_loss'])
+
+    for _ in range(3):
+        step()
+    barrier()
+    l0 = lib.b200_launch_count()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    barrier()
+    tt = torch.tensor([(time.perf_counter() - t0) / steps], device='cuda')
+    dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    dt = float(tt.item())
+    return {'samples_per_s': round(global_batch / dt, 1), 'ms_per_step': round(dt * 1e3, 3), 'global_batch': global_batch,
+            'batch_per_gpu': global_batch // world, 'scaling': 'strong',
+            'gpu_launches_per_step': int((lib.b200_launch_count() - l0) // steps),
+            'parallelism': 'dp%d: gradient all-reduce (avg) of %d parameters per layer, BatchNorm statistics '
+                           'all-reduced (avg) inside sum_t(axis=0)' % (world, net.buffer.parameters.size),
+            'timing': 'host wall clock around whole steps, max over ranks'}
+
+
 # ------------------------------------------------------------------ GPU arm
 def run_b200(args):
     world = int(os.environ.get('WORLD_SIZE', '1'))
@@ -462,6 +505,14 @@ def run_b200(args):
         ref = os.path.join(ROOT, 'baseline', '_ref')
         if os.path.isdir(os.path.join(ref, 'brainstorm')) and ref not in sys.path:
             sys.path.insert(0, ref)
+        if world > 1 and args.only == 'highway_bn':
+            res = {'highway_bn': highway_bn_sharded(H, world, rank, barrier, lib)}
+            if rank == 0:
+                print(json.dumps({'metric': 'highway_bn_train_samples_per_s',
+                                  'value': res['highway_bn'].get('samples_per_s'), 'unit': 'samples/s',
+                                  'n_gpus': world, 'detail': res}))
+            dist.destroy_process_group()
+            return
         res = other_training_configs(H, rank, lib, only=args.only)
         if rank == 0:
             print(json.dumps({'metric': '%s_train_samples_per_s' % args.only,
@@ -603,7 +654,8 @@ def run_b200(args):
 
     lstm = lstm_training(H, world, rank, max(3, min(args.steps, 10)), barrier, lib, check)
     del t, suite
-    others = other_training_configs(H, rank, lib) if world == 1 else None
+    others = other_training_configs(H, rank, lib) if world == 1 else \
+        {'highway_bn': highway_bn_sharded(H, world, rank, barrier, lib)}
 
     if rank == 0:
         peaks, peak_src = None, 'fallback'
