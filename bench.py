@@ -422,10 +422,12 @@ def other_training_configs(H, rank, lib, only=None):
     return out
 
 
-def highway_bn_sharded(H, world, rank, barrier, lib, steps=3):
-    """The Highway + BatchNorm stack with its batch of 8192 sharded over the ranks (strong
-    scaling: 8192 / world rows per GPU): gradients all-reduced per layer, BatchNorm batch
-    statistics completed across the shards inside ``sum_t(axis=0)`` (NCCL, 16 KiB each)."""
+def sharded_training(name, H, world, rank, barrier, lib):
+    """The two other training workloads on `world` GPUs.  'highway_bn': the Highway +
+    BatchNorm stack with its batch of 8192 sharded over the ranks (strong scaling, 8192 /
+    world rows per GPU); BatchNorm batch statistics are completed across the shards inside
+    ``sum_t(axis=0)`` (NCCL, 16 KiB each).  'mlp': the MNIST-style MLP with 100 samples per
+    GPU (weak scaling).  Gradients are all-reduced per layer in both."""
     try:
         import brainstorm  # noqa: F401
     except Exception as e:
@@ -434,10 +436,16 @@ def highway_bn_sharded(H, world, rank, barrier, lib, steps=3):
     import torch.distributed as dist
     from brainstorm_b200 import workloads
     from brainstorm_b200.parallel import Comm, data_parallel
-    global_batch = 8192
-    net, data, stepper = workloads.highway_bn(batch=global_batch // world, data_seed=rank)
+    if name == 'highway_bn':
+        global_batch, steps, scaling = 8192, 3, 'strong'
+        net, data, stepper = workloads.highway_bn(batch=global_batch // world, data_seed=rank)
+        reduce_mode = 'avg'
+    else:
+        global_batch, steps, scaling = 100 * world, 50, 'weak'
+        net, data, stepper = workloads.mlp(batch=100, data_seed=rank)
+        reduce_mode = 'local'
     net.set_handler(H)
-    data_parallel(net, Comm(), axis0_reduce='avg')
+    data_parallel(net, Comm(), axis0_reduce=reduce_mode)
     st = stepper()
     st.start(net)
 
@@ -458,10 +466,11 @@ def highway_bn_sharded(H, world, rank, barrier, lib, steps=3):
     dist.all_reduce(tt, op=dist.ReduceOp.MAX)
     dt = float(tt.item())
     return {'samples_per_s': round(global_batch / dt, 1), 'ms_per_step': round(dt * 1e3, 3), 'global_batch': global_batch,
-            'batch_per_gpu': global_batch // world, 'scaling': 'strong',
+            'batch_per_gpu': global_batch // world, 'scaling': scaling,
             'gpu_launches_per_step': int((lib.b200_launch_count() - l0) // steps),
-            'parallelism': 'dp%d: gradient all-reduce (avg) of %d parameters per layer, BatchNorm statistics '
-                           'all-reduced (avg) inside sum_t(axis=0)' % (world, net.buffer.parameters.size),
+            'parallelism': 'dp%d: gradient all-reduce (avg) of %d parameters per layer%s' % (
+                world, net.buffer.parameters.size,
+                ', BatchNorm statistics all-reduced (avg) inside sum_t(axis=0)' if name == 'highway_bn' else ''),
             'timing': 'host wall clock around whole steps, max over ranks'}
 
 
@@ -505,11 +514,11 @@ def run_b200(args):
         ref = os.path.join(ROOT, 'baseline', '_ref')
         if os.path.isdir(os.path.join(ref, 'brainstorm')) and ref not in sys.path:
             sys.path.insert(0, ref)
-        if world > 1 and args.only == 'highway_bn':
-            res = {'highway_bn': highway_bn_sharded(H, world, rank, barrier, lib)}
+        if world > 1:
+            res = {args.only: sharded_training(args.only, H, world, rank, barrier, lib)}
             if rank == 0:
-                print(json.dumps({'metric': 'highway_bn_train_samples_per_s',
-                                  'value': res['highway_bn'].get('samples_per_s'), 'unit': 'samples/s',
+                print(json.dumps({'metric': '%s_train_samples_per_s' % args.only,
+                                  'value': res[args.only].get('samples_per_s'), 'unit': 'samples/s',
                                   'n_gpus': world, 'detail': res}))
             dist.destroy_process_group()
             return
@@ -655,7 +664,8 @@ def run_b200(args):
     lstm = lstm_training(H, world, rank, max(3, min(args.steps, 10)), barrier, lib, check)
     del t, suite
     others = other_training_configs(H, rank, lib) if world == 1 else \
-        {'highway_bn': highway_bn_sharded(H, world, rank, barrier, lib)}
+        {'mlp': sharded_training('mlp', H, world, rank, barrier, lib),
+         'highway_bn': sharded_training('highway_bn', H, world, rank, barrier, lib)}
 
     if rank == 0:
         peaks, peak_src = None, 'fallback'
