@@ -10,6 +10,9 @@
  * Conventions
  *  - Every function returns 0 on success, non-zero otherwise; b200_last_error()
  *    then describes the failure.  Nothing traps on the device.
+ *  - One process drives one GPU, from one host thread at a time: the library keeps
+ *    per-process state (current stream, recording state, work buffers) without locks,
+ *    like the reference's handlers (one handler object per network).
  *  - Pointers are device addresses of fp32 data unless stated otherwise.  Work is
  *    queued on the library's stream in program order; only the functions marked
  *    "synchronises" wait for it.
