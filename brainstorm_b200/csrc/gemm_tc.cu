@@ -467,6 +467,329 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   if (threadIdx.x == 0 && *abort_flag && error_flag) *error_flag = 1;
 }
 
+// ---- the same GEMM on a pair of SMs --------------------------------------------------
+// tcgen05.mma.cta_group::2: two CTAs of a cluster (ranks 0 and 1, consecutive blockIdx.x)
+// compute a 256 x 256 tile together.  Each CTA stages its own 128 rows of A and HALF of
+// the B tile (128 of the 256 columns); one thread of the rank-0 CTA issues MMAs that read
+// both halves and write each CTA's 128 x 256 accumulator rows into that CTA's tensor
+// memory.  Per k-block an SM then moves 192 KB through shared memory instead of the 288 KB
+// of the 128 x 256 single-CTA tile, which is what bounds that kernel.
+//   * tcgen05.alloc / dealloc / commit all carry cta_group::2; warp 1 of BOTH CTAs
+//     allocates and frees.
+//   * "tiles split" and "accumulator drained" are counted on rank 0's barriers: the
+//     peer's warps arrive there remotely (mapa + mbarrier.arrive.shared::cluster).
+//   * "stage free" and "chunk ready" exist in both CTAs; rank 0 commits to its own
+//     barrier and to the peer's (two plain commits).
+//   * Both CTAs meet at a cluster barrier after set-up (the peer's barriers must exist
+//     before anyone arrives on them) and before tensor memory is freed.
+struct PairConfig {
+  static constexpr int A_BYTES = TC_BM * TC_BK * 4;          // this CTA's 128 rows of a
+  static constexpr int B_BYTES = 128 * TC_BK * 4;            // this CTA's 128 of the 256 columns of b
+  static constexpr int STAGE_BYTES = 2 * (A_BYTES + B_BYTES);
+  static constexpr int STAGES = 3;
+  static constexpr int BN = 256;
+  static constexpr int TMEM_COLS = 512;                      // two accumulator buffers of 256 columns
+  static constexpr int ACC = 128;                            // columns per drain group (two groups)
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+};
+
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void mma_tf32_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                              uint32_t accumulate) {
+  const uint32_t z = 0;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(z)
+      : "memory");
+}
+// bar: a shared::cluster address (this CTA's or the peer's)
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// Arrival on a barrier of this cluster (possibly the other CTA's); what this thread wrote
+// before is visible to whoever observes the phase with cluster scope.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+// Bounded wait (cluster-scope acquire) on a barrier that threads of both CTAs arrive on.
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t it = 0; it < TC_SPIN_LIMIT; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if (it > 64) {
+      if (*abort_flag) return false;
+      __nanosleep(it > 4096 ? 256 : 32);
+    }
+  }
+  *abort_flag = 1;
+  return false;
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_addr(uint32_t local_smem_addr, uint32_t cta) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem_addr), "r"(cta));
+  return remote;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
+gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                        float* __restrict__ c, int M, int N, int K, int64_t ldc, int accumulate,
+                        int a_mn_major, int b_mn_major, int* error_flag, int kb_per_split,
+                        int64_t split_stride) {
+  using Cfg = PairConfig;
+  constexpr int S = Cfg::STAGES;
+  constexpr int BN = Cfg::BN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * Cfg::STAGE_BYTES);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * S + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();          // 0 issues the MMAs
+  const bool leader = rank == 0;
+  const int m0 = blockIdx.x * TC_BM;             // this CTA's rows (the pair: blockIdx.x = 2p, 2p + 1)
+  const int n0 = blockIdx.y * BN;                // the pair's columns; this CTA stages [n0 + 128 rank, + 128)
+  const int nb0 = n0 + 128 * (int)rank;
+  const int kb_begin = blockIdx.z * kb_per_split;
+  const int num_kb = min((K + TC_BK - 1) / TC_BK - kb_begin, kb_per_split);
+  c += (int64_t)blockIdx.z * split_stride;
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto split_bar = [&](int s) { return bar0 + 8u * (S + s); };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (2 * S + s); };
+  auto acc_full_bar = [&](int b) { return bar0 + 8u * (3 * S + b); };
+  auto acc_empty_bar = [&](int b) { return bar0 + 8u * (3 * S + 2 + b); };
+  const uint32_t smem_base = smem_u32(smem);
+  auto a_hi = [&](int s) { return smem_base + s * Cfg::STAGE_BYTES; };
+  auto a_lo = [&](int s) { return a_hi(s) + Cfg::A_BYTES; };
+  auto b_hi = [&](int s) { return a_hi(s) + 2 * Cfg::A_BYTES; };
+  auto b_lo = [&](int s) { return b_hi(s) + Cfg::B_BYTES; };
+  // rank 0's copies of the two barriers that count arrivals from both CTAs
+  auto lead_split_bar = [&](int s) { return cluster_addr(split_bar(s), 0); };
+  auto lead_acc_empty_bar = [&](int b) { return cluster_addr(acc_empty_bar(b), 0); };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(split_bar(s), 256);      // the transform threads of both CTAs
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full_bar(b), 1);
+      mbar_init(acc_empty_bar(b), 512);  // both drain groups of both CTAs
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  pdl_launch_dependents();
+  if (warp == 0 && lane == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+  }
+  if (warp == 1) tmem_alloc_pair(smem_u32(tmem_slot), Cfg::TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();        // both CTAs: barriers initialised, tensor memory allocated
+  tc_fence_after();
+  const uint32_t tmem_d = *tmem_slot;
+  pdl_wait();
+
+  if (warp == 0) {
+    // ---------------- TMA producer (this CTA's tiles) ----------------
+    if (lane == 0) {
+      int issued = 0;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % S;
+        const uint32_t ph = (kb / S) & 1;
+        if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag)) break;
+        mbar_expect_tx(full_bar(s), Cfg::A_BYTES + Cfg::B_BYTES);
+        const int k0 = (kb_begin + kb) * TC_BK;
+        if (!a_mn_major) {
+          tma_load_2d(a_hi(s), &map_a, k0, m0, full_bar(s));
+        } else {
+#pragma unroll
+          for (int j = 0; j < TC_BM / 32; ++j)
+            tma_load_2d(a_hi(s) + j * (TC_BK * 128), &map_a, m0 + 32 * j, k0, full_bar(s));
+        }
+        if (!b_mn_major) {
+          tma_load_2d(b_hi(s), &map_b, k0, nb0, full_bar(s));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 128 / 32; ++j)
+            tma_load_2d(b_hi(s) + j * (TC_BK * 128), &map_b, nb0 + 32 * j, k0, full_bar(s));
+        }
+        issued = kb + 1;
+      }
+      if (*abort_flag) {
+        const int first = issued > S ? issued - S : 0;
+        for (int kb = first; kb < issued; ++kb) {
+          const uint32_t bar = full_bar(kb % S), ph = (kb / S) & 1;
+          for (uint32_t it = 0; it < TC_SPIN_LIMIT && !mbar_try_wait(bar, ph); ++it) __nanosleep(64);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------- MMA issuer: rank 0 only ----------------
+    if (leader) {
+      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(a_mn_major != 0) << 15) |
+                             ((uint32_t)(b_mn_major != 0) << 16) | ((uint32_t)(BN >> 3) << 17) |
+                             ((uint32_t)((2 * TC_BM) >> 4) << 24);
+      const uint32_t a_lbo = a_mn_major ? TC_BK * 128 : 16, b_lbo = b_mn_major ? TC_BK * 128 : 16;
+      const uint32_t a_step = a_mn_major ? 1024 : 32, b_step = b_mn_major ? 1024 : 32;
+      const uint32_t a_sbo = a_mn_major ? 512 : 1024, b_sbo = b_mn_major ? 512 : 1024;
+      const uint32_t a_lt = a_mn_major ? 1 : 2, b_lt = b_mn_major ? 1 : 2;
+      bool ok = true;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % S;
+        const uint32_t ph = (kb / S) & 1;
+        const int chunk = kb / TC_CHUNK_KB, buf = chunk & 1;
+        const bool chunk_first = (kb % TC_CHUNK_KB) == 0;
+        const bool chunk_last = (kb % TC_CHUNK_KB) == TC_CHUNK_KB - 1 || kb == num_kb - 1;
+        if (chunk_first) {
+          ok = mbar_wait_cluster(acc_empty_bar(buf), ((chunk >> 1) & 1) ^ 1, abort_flag);
+          if (!ok) break;
+        }
+        ok = mbar_wait_cluster(split_bar(s), ph, abort_flag);   // both CTAs' tiles are split
+        if (!ok) break;
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t d = tmem_d + (uint32_t)(buf * BN);
+#pragma unroll
+          for (int k = 0; k < TC_BK / 8; ++k) {
+            const uint64_t dah = smem_desc(a_hi(s) + k * a_step, a_lbo, a_sbo, a_lt);
+            const uint64_t dal = smem_desc(a_lo(s) + k * a_step, a_lbo, a_sbo, a_lt);
+            const uint64_t dbh = smem_desc(b_hi(s) + k * b_step, b_lbo, b_sbo, b_lt);
+            const uint64_t dbl = smem_desc(b_lo(s) + k * b_step, b_lbo, b_sbo, b_lt);
+            mma_tf32_pair(d, dal, dbh, idesc, !(chunk_first && k == 0));
+            mma_tf32_pair(d, dah, dbl, idesc, 1);
+            mma_tf32_pair(d, dah, dbh, idesc, 1);
+          }
+          mma_commit_pair(empty_bar(s));                       // this CTA's stage ...
+          mma_commit_pair(cluster_addr(empty_bar(s), 1));      // ... and the peer's
+          if (chunk_last) {
+            mma_commit_pair(acc_full_bar(buf));
+            mma_commit_pair(cluster_addr(acc_full_bar(buf), 1));
+          }
+        }
+        __syncwarp();
+      }
+    }
+    __syncwarp();
+  } else if (warp < 6) {
+    // ---------------- split transform + drain of columns [0, 128) ----------------
+    const int t = threadIdx.x - 64;
+    const int q = warp & 3;
+    const uint32_t lane_bits = (uint32_t)(q * 32) << 16;
+    const int num_chunks = (num_kb + TC_CHUNK_KB - 1) / TC_CHUNK_KB;
+    float acc[Cfg::ACC];
+#pragma unroll
+    for (int j = 0; j < Cfg::ACC; ++j) acc[j] = 0.f;
+    int next_chunk = 0;
+    bool ok = true;
+    auto drain = [&](int chunk_idx) {
+      const int buf = chunk_idx & 1;
+      tc_fence_after();
+      drain_add<Cfg::ACC>(tmem_d + lane_bits + (uint32_t)(buf * BN), acc);
+      tc_fence_before();
+      mbar_arrive_cluster(lead_acc_empty_bar(buf));
+    };
+    for (int kb = 0; kb < num_kb && ok; ++kb) {
+      const int s = kb % S;
+      const uint32_t ph = (kb / S) & 1;
+      ok = mbar_wait(full_bar(s), ph, abort_flag);
+      if (!ok) break;
+      const float4* ah = reinterpret_cast<const float4*>(smem + s * Cfg::STAGE_BYTES);
+      float4* al = reinterpret_cast<float4*>(smem + s * Cfg::STAGE_BYTES + Cfg::A_BYTES);
+      const float4* bh = reinterpret_cast<const float4*>(smem + s * Cfg::STAGE_BYTES + 2 * Cfg::A_BYTES);
+      float4* bl = reinterpret_cast<float4*>(smem + s * Cfg::STAGE_BYTES + 2 * Cfg::A_BYTES + Cfg::B_BYTES);
+#pragma unroll
+      for (int i = 0; i < Cfg::A_BYTES / 16 / 128; ++i) {
+        const float4 v = ah[t + 128 * i];
+        al[t + 128 * i] = make_float4(tf32_residual(v.x), tf32_residual(v.y), tf32_residual(v.z), tf32_residual(v.w));
+      }
+#pragma unroll
+      for (int i = 0; i < Cfg::B_BYTES / 16 / 128; ++i) {
+        const float4 v = bh[t + 128 * i];
+        bl[t + 128 * i] = make_float4(tf32_residual(v.x), tf32_residual(v.y), tf32_residual(v.z), tf32_residual(v.w));
+      }
+      fence_async_smem();
+      mbar_arrive_cluster(lead_split_bar(s));
+      while (next_chunk < num_chunks) {   // drain what has finished, never wait for what has not
+        const bool ready = __all_sync(0xffffffffu, mbar_test_wait(acc_full_bar(next_chunk & 1), (next_chunk >> 1) & 1));
+        if (!ready) break;
+        drain(next_chunk);
+        ++next_chunk;
+      }
+    }
+    for (; next_chunk < num_chunks && ok; ++next_chunk) {
+      ok = mbar_wait(acc_full_bar(next_chunk & 1), (next_chunk >> 1) & 1, abort_flag);
+      __syncwarp();
+      if (!ok) break;
+      drain(next_chunk);
+    }
+    if (ok) {
+      float* sbuf = reinterpret_cast<float*>(smem) + (warp - 2) * 32 * (Cfg::ACC + 4);
+      store_tile<Cfg::ACC>(acc, sbuf, c, ldc, m0 + q * 32, n0, M, N, accumulate);
+    }
+  } else {
+    // ---------------- drain of columns [128, 256), then epilogue ----------------
+    const int q = warp & 3;
+    const uint32_t lane_bits = (uint32_t)(q * 32) << 16;
+    float acc[Cfg::ACC];
+#pragma unroll
+    for (int j = 0; j < Cfg::ACC; ++j) acc[j] = 0.f;
+    const int num_chunks = (num_kb + TC_CHUNK_KB - 1) / TC_CHUNK_KB;
+    bool ok = true;
+    for (int chunk = 0; chunk < num_chunks && ok; ++chunk) {
+      const int buf = chunk & 1;
+      ok = mbar_wait(acc_full_bar(buf), (chunk >> 1) & 1, abort_flag);
+      __syncwarp();
+      if (!ok) break;
+      tc_fence_after();
+      drain_add<Cfg::ACC>(tmem_d + lane_bits + (uint32_t)(buf * BN + Cfg::ACC), acc);
+      tc_fence_before();
+      mbar_arrive_cluster(lead_acc_empty_bar(buf));
+    }
+    if (ok) {
+      float* sbuf = reinterpret_cast<float*>(smem) + (4 + warp - 6) * 32 * (Cfg::ACC + 4);
+      store_tile<Cfg::ACC>(acc, sbuf, c, ldc, m0 + q * 32, n0 + Cfg::ACC, M, N, accumulate);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();        // nobody in the pair reads shared or tensor memory of the other any more
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_d, Cfg::TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && *abort_flag && error_flag) *error_flag = 1;
+}
+
 // out[m, n] (+)= sum over splits of partial[s][m][n], splits added in index order.
 __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(const float* __restrict__ partial, int splits, int64_t split_stride, float* out,
@@ -570,6 +893,7 @@ static int tc_setup() {
   B200_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcConfig<64>::SMEM_BYTES));
   B200_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcConfig<128>::SMEM_BYTES));
   B200_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcConfig<256>::SMEM_BYTES));
+  B200_CUDA(cudaFuncSetAttribute(gemm_tf32x3_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairConfig::SMEM_BYTES));
   h.encode = (EncodeTiledFn)fn;
   return B200_OK;
 }
@@ -713,10 +1037,37 @@ static int gemm_tc_impl(int transa, int transb, int64_t M, int64_t N, int64_t K,
   // B: K-major when transposed (array is N x K), MN-major when not (K x N)
   if (int rc = transb ? tc_map(b, K, N, ldb, bn, 0, &mb) : tc_map(b, N, K, ldb, TC_BK, 1, &mb)) { release(&sa); release(&sb); return rc; }
   dim3 grid((unsigned)ceil_div(N, bn), (unsigned)tiles_m, (unsigned)splits);
+  const bool pair = bn == 256 && s.gemm_pair;
+  if (pair)   // CTA pairs along x = M (rows past M are zero-filled and not stored), column tiles along y
+    grid = dim3((unsigned)(ceil_div(tiles_m, 2) * 2), (unsigned)ceil_div(N, bn), (unsigned)splits);
   int* flag = tc_host().error_flag_dev;
   const int m = (int)M, n = (int)N, k = (int)K;
   const int amn = transa ? 1 : 0, bmn = transb ? 0 : 1;
-  switch (bn) {
+  if (pair) {
+    CUtensorMap mbh;   // the pair's b tile arrives as two halves of 128 columns, one per CTA
+    if (int rc = transb ? tc_map(b, K, N, ldb, 128, 0, &mbh) : tc_map(b, N, K, ldb, TC_BK, 1, &mbh)) { release(&sa); release(&sb); return rc; }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = PairConfig::SMEM_BYTES;
+    cfg.stream = s.stream;
+    cudaLaunchAttribute attr[1];     // the cluster shape (2 x 1 x 1) is part of the kernel's declaration
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = s.pdl_now ? 1 : 0;
+    const cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_tf32x3_pair_kernel, ma, mbh, dst, m, n, k, dst_ld, acc_flag, amn,
+                                              bmn, flag, kb_per_split, split_stride);
+    if (le != cudaSuccess) {
+      int clusters = -1;
+      cudaOccupancyMaxActiveClusters(&clusters, gemm_tf32x3_pair_kernel, &cfg);
+      cudaGetLastError();
+      release(&sa); release(&sb);
+      return set_error(B200_ERR_CUDA, "pair GEMM launch failed: %s (grid %u x %u x %u, cluster 2 x 1 x 1, %d bytes of "
+                       "shared memory, %d clusters can be resident)", cudaGetErrorString(le), grid.x, grid.y, grid.z,
+                       (int)PairConfig::SMEM_BYTES, clusters);
+    }
+  } else switch (bn) {
     case 32: B200_CUDA(launch_maybe_pdl(s.pdl_now, gemm_tf32x3_kernel<32>, grid, dim3(TC_THREADS), (size_t)TcConfig<32>::SMEM_BYTES, s.stream, ma, mb, dst, m, n, k, dst_ld, acc_flag, amn, bmn, flag, kb_per_split, split_stride)); break;
     case 64: B200_CUDA(launch_maybe_pdl(s.pdl_now, gemm_tf32x3_kernel<64>, grid, dim3(TC_THREADS), (size_t)TcConfig<64>::SMEM_BYTES, s.stream, ma, mb, dst, m, n, k, dst_ld, acc_flag, amn, bmn, flag, kb_per_split, split_stride)); break;
     case 256: B200_CUDA(launch_maybe_pdl(s.pdl_now, gemm_tf32x3_kernel<256>, grid, dim3(TC_THREADS), (size_t)TcConfig<256>::SMEM_BYTES, s.stream, ma, mb, dst, m, n, k, dst_ld, acc_flag, amn, bmn, flag, kb_per_split, split_stride)); break;

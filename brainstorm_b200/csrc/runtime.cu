@@ -112,6 +112,7 @@ B200_API int b200_set_tuning(int key, int value) {
     case 2: B200_REQUIRE(value >= 0 && value <= 2, "gemm path must be 0, 1 or 2"); s.gemm_path = value; break;
     case 3: s.gemm_bn = value; break;
     case 5: s.use_pdl = value ? 1 : 0; break;
+    case 7: s.gemm_pair = value ? 1 : 0; break;
     case 6: B200_REQUIRE(value >= 1 && value <= 8, "SM share divisor out of range"); s.sm_share = value; break;
     default: return set_error(B200_ERR_ARG, "unknown tuning key %d", key);
   }

@@ -40,7 +40,9 @@ int b200_device_info(int* device, int* sm_count, uint64_t* free_bytes, uint64_t*
 /* key 0: elementwise blocks per SM; 1: elementwise threads per block;
  * 2: GEMM path (0 auto, 1 CUDA cores, 2 tensor cores only); 3: forced GEMM tile width;
  * 5: programmatic dependent launch inside the LSTM time loops (default 1);
- * 6: split-K plans for 1/value of the SMs (default 1; 2 while two streams share the GPU). */
+ * 6: split-K plans for 1/value of the SMs (default 1; 2 while two streams share the GPU);
+ * 7: 256-wide GEMM tiles on pairs of SMs (tcgen05 cta_group::2; default 0: measured slower
+ *    than the single-SM tiles so far). */
 int b200_set_tuning(int key, int value);
 uint64_t b200_stream(void);                            /* the main stream (a cudaStream_t) */
 /* A second compute stream, for work that may run beside the main stream's (a stack of
