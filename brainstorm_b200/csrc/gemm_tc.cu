@@ -176,6 +176,26 @@ __device__ __forceinline__ float tf32_residual(float x) {
   return x - __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
 }
 
+// Residual tile of a landed tile, done by 128 threads: lo[i] = residual(hi[i]) for the
+// NV float4 of this thread (thread t owns float4 t, t + 128, ...).  All loads of a batch
+// of eight are issued before the first store, so their latencies overlap (the compiler
+// cannot reorder them itself: the two buffers may alias for all it knows).
+template <int NV>
+__device__ __forceinline__ void split_tile(const float4* __restrict__ hi, float4* __restrict__ lo, int t) {
+  constexpr int BATCH = NV < 8 ? NV : 8;
+  static_assert(NV % BATCH == 0, "tile size");
+#pragma unroll
+  for (int i0 = 0; i0 < NV; i0 += BATCH) {
+    float4 v[BATCH];
+#pragma unroll
+    for (int i = 0; i < BATCH; ++i) v[i] = hi[t + 128 * (i0 + i)];
+#pragma unroll
+    for (int i = 0; i < BATCH; ++i)
+      lo[t + 128 * (i0 + i)] = make_float4(tf32_residual(v[i].x), tf32_residual(v[i].y), tf32_residual(v[i].z),
+                                           tf32_residual(v[i].w));
+  }
+}
+
 // acc[0..NCOLS) += the NCOLS accumulator columns at taddr of this warp's TMEM lanes
 template <int NCOLS>
 __device__ __forceinline__ void drain_add(uint32_t taddr, float (&acc)[NCOLS]) {
@@ -386,16 +406,8 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       float4* al = reinterpret_cast<float4*>(smem + s * Cfg::STAGE_BYTES + Cfg::A_BYTES);
       const float4* bh = reinterpret_cast<const float4*>(smem + s * Cfg::STAGE_BYTES + 2 * Cfg::A_BYTES);
       float4* bl = reinterpret_cast<float4*>(smem + s * Cfg::STAGE_BYTES + 2 * Cfg::A_BYTES + Cfg::B_BYTES);
-#pragma unroll
-      for (int i = 0; i < Cfg::A_BYTES / 16 / 128; ++i) {
-        const float4 v = ah[t + 128 * i];
-        al[t + 128 * i] = make_float4(tf32_residual(v.x), tf32_residual(v.y), tf32_residual(v.z), tf32_residual(v.w));
-      }
-#pragma unroll
-      for (int i = 0; i < Cfg::B_BYTES / 16 / 128; ++i) {
-        const float4 v = bh[t + 128 * i];
-        bl[t + 128 * i] = make_float4(tf32_residual(v.x), tf32_residual(v.y), tf32_residual(v.z), tf32_residual(v.w));
-      }
+      split_tile<Cfg::A_BYTES / 16 / 128>(ah, al, t);
+      split_tile<Cfg::B_BYTES / 16 / 128>(bh, bl, t);
       fence_async_smem();   // generic-proxy writes -> visible to the tensor core's async reads
       mbar_arrive(split_bar(s));
       if (kDrainsToo) {
@@ -727,16 +739,8 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
       float4* al = reinterpret_cast<float4*>(smem + s * Cfg::STAGE_BYTES + Cfg::A_BYTES);
       const float4* bh = reinterpret_cast<const float4*>(smem + s * Cfg::STAGE_BYTES + 2 * Cfg::A_BYTES);
       float4* bl = reinterpret_cast<float4*>(smem + s * Cfg::STAGE_BYTES + 2 * Cfg::A_BYTES + Cfg::B_BYTES);
-#pragma unroll
-      for (int i = 0; i < Cfg::A_BYTES / 16 / 128; ++i) {
-        const float4 v = ah[t + 128 * i];
-        al[t + 128 * i] = make_float4(tf32_residual(v.x), tf32_residual(v.y), tf32_residual(v.z), tf32_residual(v.w));
-      }
-#pragma unroll
-      for (int i = 0; i < Cfg::B_BYTES / 16 / 128; ++i) {
-        const float4 v = bh[t + 128 * i];
-        bl[t + 128 * i] = make_float4(tf32_residual(v.x), tf32_residual(v.y), tf32_residual(v.z), tf32_residual(v.w));
-      }
+      split_tile<Cfg::A_BYTES / 16 / 128>(ah, al, t);
+      split_tile<Cfg::B_BYTES / 16 / 128>(bh, bl, t);
       fence_async_smem();
       mbar_arrive_cluster(lead_split_bar(s));
       while (next_chunk < num_chunks) {   // drain what has finished, never wait for what has not
