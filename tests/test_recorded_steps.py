@@ -254,3 +254,95 @@ def test_graphed_mlp_with_dropout_learns_and_uses_fresh_masks():
         gs.run()
         masks.append(net.get('%s.internals.mask' % name))
     assert not np.array_equal(masks[-1], masks[-2])
+
+
+# ------------------------------------------------------------------ GraphedStepper logic, no GPU
+class _FakeStep(object):
+    def __init__(self):
+        self.launches, self.released = 0, False
+
+    def launch(self):
+        assert not self.released
+        self.launches += 1
+
+    def release(self):
+        self.released = True
+
+
+class _FakeArray(object):
+    def __init__(self, ptr):
+        self.ptr = ptr
+
+
+class _FakeManager(object):
+    def __init__(self):
+        self.full_buffer, self.time_size, self.batch_size = _FakeArray(4096), 5, 16
+
+
+class _FakeNet(object):
+    def __init__(self):
+        self._buffer_manager = _FakeManager()
+        self.handler = type('H', (), {'_comm': None})()
+
+
+class _FakeStepper(object):
+    def __init__(self):
+        self.learning_rate, self._runs, self.net = 0.1, 0, None   # scalars without '_' are part of the key
+
+    def start(self, net):
+        self.net = net
+
+    def run(self):
+        self._runs += 1
+
+
+def _graphed(monkeypatch):
+    from brainstorm_b200 import graph
+    made = []
+
+    def fake_record(fn, *a, **k):
+        fn(*a, **k)                      # a recording runs the calls once (without executing them)
+        made.append(_FakeStep())
+        return made[-1]
+
+    monkeypatch.setattr(graph, 'record', fake_record)
+    inner = _FakeStepper()
+    gs = graph.GraphedStepper(inner, eager_steps=1)
+    net = _FakeNet()
+    gs.start(net)
+    return gs, inner, net, made
+
+
+def test_graphed_stepper_runs_once_eagerly_then_records_then_replays(monkeypatch):
+    gs, inner, net, made = _graphed(monkeypatch)
+    for _ in range(5):
+        gs.run()
+    assert inner._runs == 2               # the eager step and the recorded one
+    assert len(made) == 1 and made[0].launches == 4
+
+
+def test_graphed_stepper_records_again_after_a_change_of_scalar_shape_or_buffer(monkeypatch):
+    gs, inner, net, made = _graphed(monkeypatch)
+    for _ in range(3):
+        gs.run()
+    inner.learning_rate = 0.05
+    for _ in range(3):
+        gs.run()
+    net._buffer_manager.batch_size = 8
+    for _ in range(3):
+        gs.run()
+    net._buffer_manager.full_buffer = _FakeArray(8192)
+    for _ in range(3):
+        gs.run()
+    assert len(made) == 4
+    assert [m.released for m in made] == [True, True, True, False]
+    assert all(m.launches == 2 for m in made)       # per setting: eager, record + launch, launch
+    assert inner._runs == 8
+
+
+def test_graphed_stepper_passes_through_under_data_parallelism(monkeypatch):
+    gs, inner, net, made = _graphed(monkeypatch)
+    net.handler._comm = object()
+    for _ in range(4):
+        gs.run()
+    assert inner._runs == 4 and not made
