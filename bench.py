@@ -468,8 +468,8 @@ def sharded_training(name, H, world, rank, barrier, lib):
     return {'samples_per_s': round(global_batch / dt, 1), 'ms_per_step': round(dt * 1e3, 3), 'global_batch': global_batch,
             'batch_per_gpu': global_batch // world, 'scaling': scaling,
             'gpu_launches_per_step': int((lib.b200_launch_count() - l0) // steps),
-            'parallelism': 'dp%d: gradient all-reduce (avg) of %d parameters per layer%s' % (
-                world, net.buffer.parameters.size,
+            'parallelism': 'dp%d: gradient all-reduce (avg) of %d parameters, %s%s' % (
+                world, net.buffer.parameters.size, 'per layer' if name == 'highway_bn' else 'in one piece',
                 ', BatchNorm statistics all-reduced (avg) inside sum_t(axis=0)' if name == 'highway_bn' else ''),
             'timing': 'host wall clock around whole steps, max over ranks'}
 

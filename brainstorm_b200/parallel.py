@@ -153,6 +153,9 @@ def _element_offset(view, flat):
     return (view.ptr - flat.ptr) // 4
 
 
+OVERLAP_MIN_BYTES = 32 << 20     # gradient vectors below this are all-reduced in one piece
+
+
 def data_parallel(net, comm, axis0_reduce='local', overlap=True):
     """Make ``net`` (already on its handler) train data-parallel over ``comm``.
 
@@ -186,7 +189,10 @@ def data_parallel(net, comm, axis0_reduce='local', overlap=True):
 
     net.backward_pass = backward_pass
 
-    if overlap and hasattr(comm, 'allreduce_async') and not getattr(net, 'gradient_modifiers', None):
+    # Small networks are bound by the host: one collective over the whole vector costs fewer
+    # calls than one per layer, and there is nothing worth overlapping.
+    big_enough = net.buffer.gradients.size * 4 >= OVERLAP_MIN_BYTES
+    if overlap and big_enough and hasattr(comm, 'allreduce_async') and not getattr(net, 'gradient_modifiers', None):
         def wrap(name, layer):
             layer_backward = layer.backward_pass
 

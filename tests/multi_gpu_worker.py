@@ -22,6 +22,7 @@ def main():
     from brainstorm.handlers import NumpyHandler
     from brainstorm_b200 import B200Handler, workloads
     from brainstorm_b200.fused_lstm import fuse_lstm_layers
+    from brainstorm_b200 import parallel
     from brainstorm_b200.parallel import Comm, data_parallel, shard_batch
     from brainstorm_b200.workloads import train_steps
     H = B200Handler(seed=3, device=local)
@@ -33,6 +34,8 @@ def main():
         net.set_handler(H)
         if which == 'lstm':
             fuse_lstm_layers(net)
+        # one network with an all-reduce per layer (what large networks get), one with a single one
+        parallel.OVERLAP_MIN_BYTES = 0 if which == 'highway_bn' else (1 << 40)
         data_parallel(net, Comm(), axis0_reduce=mode)
         losses = train_steps(net, shard_batch(data, rank, world), stepper(), 3)
         params = net.get('parameters')

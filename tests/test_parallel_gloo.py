@@ -83,10 +83,13 @@ def _build(which):
     return workloads.mlp(batch=16, hidden=24, n_in=20, n_out=4)
 
 
-def _rank_train(rank, port, which, out_dir):
+def _rank_train(rank, port, which, out_dir, per_layer=True):
     dist = _init(rank, port)
     from brainstorm.handlers import NumpyHandler
+    from brainstorm_b200 import parallel
     from brainstorm_b200.parallel import Comm, AxisZeroAllReduce, data_parallel, shard_batch
+    # per layer (the form large networks get) or one all-reduce over the whole vector
+    parallel.OVERLAP_MIN_BYTES = 0 if per_layer else (1 << 40)
     from brainstorm_b200.workloads import train_steps
 
     class ShardedNumpyHandler(AxisZeroAllReduce, NumpyHandler):
@@ -102,11 +105,12 @@ def _rank_train(rank, port, which, out_dir):
 
 
 @needs_reference
+@pytest.mark.parametrize('per_layer', [True, False], ids=['per-layer', 'one-piece'])
 @pytest.mark.parametrize('which', ['lstm', 'highway_bn'])
-def test_sharded_training_equals_global_batch(tmp_path, which):
+def test_sharded_training_equals_global_batch(tmp_path, which, per_layer):
     from brainstorm.handlers import NumpyHandler
     from brainstorm_b200.workloads import train_steps
-    _spawn(_rank_train, which, str(tmp_path))
+    _spawn(_rank_train, which, str(tmp_path), per_layer)
     net, data, stepper = _build(which)
     net.set_handler(NumpyHandler(np.float64))
     losses = train_steps(net, data, stepper(), 3)
