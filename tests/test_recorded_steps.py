@@ -256,6 +256,36 @@ def test_graphed_mlp_with_dropout_learns_and_uses_fresh_masks():
     assert not np.array_equal(masks[-1], masks[-2])
 
 
+@pytest.mark.gpu
+@needs_reference
+def test_reference_trainer_runs_on_a_graphed_stepper():
+    """The reference's Trainer with hooks and a Minibatches iterator, its stepper wrapped in
+    GraphedStepper: same logs and parameters as with the plain stepper, bit for bit, and
+    the wrapper survives the Trainer's description machinery."""
+    import brainstorm as bs
+    from brainstorm.describable import get_description
+    from brainstorm_b200 import B200Handler, GraphedStepper, workloads
+    rs = np.random.RandomState(2)
+    T, B, V = 5, 8, 9
+    x = np.eye(V, dtype=np.float32)[rs.randint(0, V, (T, 4 * B))]
+    tgt = rs.randint(0, V, (T, 4 * B, 1)).astype(np.int32)
+    results = []
+    for wrap in (lambda s: s, GraphedStepper):
+        net, _, _ = workloads.lstm(time=T, batch=B, vocab=V, hidden=12, layers=1)
+        net.set_handler(B200Handler(seed=1))
+        stepper = wrap(bs.training.SgdStepper(learning_rate=0.1))
+        trainer = bs.Trainer(stepper, verbose=False)
+        trainer.add_hook(bs.hooks.StopOnNan())
+        trainer.add_hook(bs.hooks.StopAfterEpoch(3))
+        trainer.train(net, bs.data_iterators.Minibatches(B, shuffle=False, default=x, targets=tgt))
+        assert trainer.current_update_nr == 12
+        results.append((list(trainer.logs['rolling_training']['total_loss']), net.get('parameters')))
+    assert stepper._step is not None and stepper._step.kernels > 10
+    assert get_description(stepper)['@type'] == 'GraphedStepper'
+    assert results[0][0] == results[1][0]
+    assert np.array_equal(results[0][1], results[1][1])
+
+
 # ------------------------------------------------------------------ GraphedStepper logic, no GPU
 class _FakeStep(object):
     def __init__(self):
