@@ -928,14 +928,24 @@ static int tc_map(const float* p, int64_t inner, int64_t outer, int64_t ld, int 
   return B200_OK;
 }
 
-// Reports (and clears) a timeout raised by a tensor-core kernel.  Called by the
-// synchronising entry points after the stream has drained.
+// The device-visible word that kernels with bounded waits raise when they give up
+// (mapped host memory; NULL if it cannot be set up).
+int* device_error_flag() {
+  std::lock_guard<std::mutex> lock(tc_host().mu);
+  if (tc_setup() != B200_OK) return nullptr;
+  return tc_host().error_flag_dev;
+}
+
+// Reports (and clears) a timeout raised by a kernel (a tensor-core GEMM waiting on a
+// barrier, a peer all-reduce waiting for another rank).  Called by the synchronising
+// entry points after the stream has drained.
 int gemm_tc_check_flag() {
   TcHost& h = tc_host();
   if (h.error_flag_host && *h.error_flag_host) {
     *h.error_flag_host = 0;
     return set_error(B200_ERR_DEVICE_FLAG,
-                     "a tensor-core GEMM gave up waiting on a barrier; its output is invalid");
+                     "a kernel gave up waiting (a tensor-core GEMM on a barrier, or a peer all-reduce on another "
+                     "rank); its output is invalid");
   }
   return B200_OK;
 }

@@ -1,0 +1,187 @@
+// All-reduce of small arrays over NVLink peer memory, one kernel per call.
+//
+// The exchanges on the handler path that sit next to a reduction are small: the sums
+// over the batch axis that sum_t(axis=0) completes across the batch shards (BatchNorm
+// statistics, the op suite's axis-0 sum) are a few thousand floats.  A library
+// collective costs tens of microseconds of launch and protocol for them.  Here every
+// rank (one process per GPU) owns a "window" of device memory that all other ranks of
+// the node have mapped (cudaIpc): two data slots and one arrival counter per rank.  One
+// CTA per call
+//   1. copies the local values into this rank's slot of the current epoch's parity,
+//   2. publishes the epoch to every rank's counter array (system-scope release store
+//      over NVLink),
+//   3. waits until all ranks have published this epoch (bounded spin on local memory),
+//   4. adds the slots of all ranks in rank order -- the same order on every rank, so all
+//      replicas get the same bits -- and writes the result.
+// Two slots suffice: a rank can only be one epoch ahead of the slowest one, because its
+// next wait needs everybody's next publication, which follows their reads of this epoch.
+// Plain peer loads and stores only; no multimem, no NCCL.  The wait is bounded (about a
+// second); on a timeout the kernel raises the library's device error flag and returns.
+//
+// Kernels of different ranks wait for one another, so every rank must run on its own
+// GPU (one process per GPU, as everywhere in this library).
+#include <string.h>
+
+#include "common.cuh"
+
+namespace b200 {
+
+int* device_error_flag();   // gemm_tc.cu: mapped host word reported at the next synchronisation
+
+constexpr int PEER_MAX_RANKS = 16;
+constexpr int PEER_MAX_FLOATS = 65536;                  // per call: 256 KiB per slot
+constexpr size_t PEER_SLOT_BYTES = (size_t)PEER_MAX_FLOATS * sizeof(float);
+constexpr size_t PEER_COUNTER_OFFSET = 2 * PEER_SLOT_BYTES;
+constexpr size_t PEER_WINDOW_BYTES = PEER_COUNTER_OFFSET + 256;   // counters: PEER_MAX_RANKS x 8 bytes, padded
+
+struct PeerState {
+  int rank = -1, world = 0;
+  uint8_t* window[PEER_MAX_RANKS] = {};   // [rank] = own window, others = mapped peers
+  unsigned long long epoch = 0;           // host copy of the call counter
+} g_peer;
+
+struct PeerArgs {
+  uint8_t* window[PEER_MAX_RANKS];
+  int rank, world;
+};
+
+__device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__global__ void __launch_bounds__(1024)
+peer_allreduce_kernel(PeerArgs a, const float* src, float* dst, int n, int average,   // dst may be src
+                      unsigned long long epoch, int* error_flag) {
+  __shared__ int timed_out;
+  const int slot = (int)(epoch & 1);
+  float* mine = reinterpret_cast<float*>(a.window[a.rank] + slot * PEER_SLOT_BYTES);
+  if (threadIdx.x == 0) timed_out = 0;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) mine[i] = src[i];
+  __threadfence_system();     // the slot is written before the epoch is published
+  __syncthreads();
+  if (threadIdx.x < a.world) {
+    unsigned long long* counters = reinterpret_cast<unsigned long long*>(a.window[threadIdx.x] + PEER_COUNTER_OFFSET);
+    st_release_sys(counters + a.rank, epoch);
+  }
+  if (threadIdx.x < a.world) {
+    const unsigned long long* counters =
+        reinterpret_cast<const unsigned long long*>(a.window[a.rank] + PEER_COUNTER_OFFSET);
+    bool seen = false;
+    for (unsigned it = 0; it < (1u << 22) && !seen; ++it) {      // about a second with the back-off below
+      seen = ld_acquire_sys(counters + threadIdx.x) >= epoch;
+      if (!seen && it > 32) __nanosleep(200);
+    }
+    if (!seen) timed_out = 1;
+  }
+  __syncthreads();
+  if (timed_out) {
+    if (threadIdx.x == 0 && error_flag) *error_flag = 1;
+    return;                   // dst is left as it was; the host reports the flag
+  }
+  const float scale = average ? 1.0f / (float)a.world : 1.0f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float acc = 0.f;
+    for (int r = 0; r < a.world; ++r) {
+      const float* theirs = reinterpret_cast<const float*>(a.window[r] + slot * PEER_SLOT_BYTES);
+      const float v = __ldcv(theirs + i);     // not cached: written by another GPU
+      acc = (r == 0) ? v : __fadd_rn(acc, v);
+    }
+    dst[i] = average ? __fmul_rn(acc, scale) : acc;
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// Size of the window every rank allocates (b200_peer_window_alloc) and exports.
+B200_API uint64_t b200_peer_window_bytes(void) { return PEER_WINDOW_BYTES; }
+B200_API int b200_peer_max_floats(void) { return PEER_MAX_FLOATS; }
+
+// The window of this rank: plain cudaMalloc memory (stream-ordered pool memory cannot
+// be exported), zeroed.  `handle` receives the 64 bytes other processes open.
+B200_API int b200_peer_window_alloc(uint64_t* ptr, void* handle) {
+  if (int rc = require_ready()) return rc;
+  B200_REQUIRE(ptr != nullptr && handle != nullptr, "NULL argument");
+  void* p = nullptr;
+  B200_CUDA(cudaMalloc(&p, PEER_WINDOW_BYTES));
+  B200_CUDA(cudaMemset(p, 0, PEER_WINDOW_BYTES));
+  cudaIpcMemHandle_t h;
+  const cudaError_t e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    return cuda_fail(e, "cudaIpcGetMemHandle", __FILE__, __LINE__);
+  }
+  static_assert(sizeof(h) == 64, "IPC handle size");
+  memcpy(handle, &h, sizeof(h));
+  *ptr = (uint64_t)(uintptr_t)p;
+  return B200_OK;
+}
+
+// Maps the window another process of this node exported.
+B200_API int b200_peer_window_open(const void* handle, uint64_t* ptr) {
+  if (int rc = require_ready()) return rc;
+  B200_REQUIRE(ptr != nullptr && handle != nullptr, "NULL argument");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  void* p = nullptr;
+  B200_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+  *ptr = (uint64_t)(uintptr_t)p;
+  return B200_OK;
+}
+
+// windows[r] for r in [0, world): this rank's own window at [rank], the mapped ones elsewhere.
+B200_API int b200_peer_setup(int rank, int world, const uint64_t* windows) {
+  if (int rc = require_ready()) return rc;
+  B200_REQUIRE(world >= 1 && world <= PEER_MAX_RANKS && rank >= 0 && rank < world && windows != nullptr,
+               "bad rank / world (at most %d ranks)", PEER_MAX_RANKS);
+  g_peer.rank = rank;
+  g_peer.world = world;
+  g_peer.epoch = 0;
+  for (int r = 0; r < world; ++r) g_peer.window[r] = (uint8_t*)(uintptr_t)windows[r];
+  return B200_OK;
+}
+
+// Unmaps the peers' windows and frees this rank's.  All ranks must have finished their
+// last b200_peer_allreduce (synchronise, then a host barrier) before any rank calls this.
+B200_API int b200_peer_teardown(void) {
+  if (g_peer.world == 0) return B200_OK;
+  for (int r = 0; r < g_peer.world; ++r) {
+    if (!g_peer.window[r]) continue;
+    if (r == g_peer.rank) cudaFree(g_peer.window[r]);
+    else cudaIpcCloseMemHandle(g_peer.window[r]);
+    g_peer.window[r] = nullptr;
+  }
+  g_peer.world = 0;
+  g_peer.rank = -1;
+  return B200_OK;
+}
+
+// dst[i] = sum over ranks of src[i] (or the mean), n <= b200_peer_max_floats().  Every rank
+// calls it in the same order with the same n; dst may be src.  Queued on the library's
+// current stream like any other kernel; a rank that never arrives makes the others give up
+// after about a second and raise the device error flag (reported by the next
+// synchronising call).
+B200_API int b200_peer_allreduce(const float* src, float* dst, int n, int average) {
+  if (int rc = require_ready()) return rc;
+  B200_REQUIRE(g_peer.world > 0, "b200_peer_setup has not been called");
+  B200_REQUIRE(n >= 0 && n <= PEER_MAX_FLOATS, "at most %d floats per call", PEER_MAX_FLOATS);
+  if (n == 0) return B200_OK;
+  B200_REQUIRE(src != nullptr && dst != nullptr, "NULL operand");
+  B200_REQUIRE(!state().capturing, "a peer all-reduce cannot be recorded into a graph (its epoch is a call argument)");
+  PeerArgs a;
+  for (int r = 0; r < PEER_MAX_RANKS; ++r) a.window[r] = g_peer.window[r];
+  a.rank = g_peer.rank;
+  a.world = g_peer.world;
+  const unsigned long long epoch = ++g_peer.epoch;
+  int threads = (n + 31) / 32 * 32;          // at least one warp (the ranks' counters are handled by threads 0..world-1)
+  if (threads > 1024) threads = 1024;
+  peer_allreduce_kernel<<<1, threads, 0, state().stream>>>(a, src, dst, n, average, epoch, device_error_flag());
+  B200_LAUNCH_CHECK();
+  return B200_OK;
+}

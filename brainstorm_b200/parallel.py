@@ -36,6 +36,58 @@ class Comm(object):
         self.world = dist.get_world_size()
         self.rank = dist.get_rank()
         self._stream = None
+        self._peer_max = 0        # > 0: device arrays up to this many floats go over peer memory
+
+    def enable_peer(self):
+        """Set up the library's all-reduce over NVLink peer memory for small device
+        arrays (``b200_peer_allreduce``: one single-CTA kernel per call instead of a
+        library collective; the sums that complete ``sum_t(axis=0)`` across batch shards
+        are a few thousand floats).  Collective: every rank calls it.  Needs one process
+        per GPU on one node and CUDA IPC between them; returns False, and leaves
+        everything on NCCL, if any rank cannot set it up."""
+        import ctypes
+        from ._lib import lib
+        if self.world == 1 or self._peer_max:
+            return bool(self._peer_max)
+        if self.world > 16:
+            return False
+        handle = ctypes.create_string_buffer(64)
+        mine = ctypes.c_uint64()
+        ok = lib.b200_peer_window_alloc(ctypes.byref(mine), handle) == 0
+        gathered = [None] * self.world
+        self.dist.all_gather_object(gathered, (ok, handle.raw if ok else None))
+        ok = all(g[0] for g in gathered)
+        windows = (ctypes.c_uint64 * self.world)()
+        if ok:
+            for r, (_, raw) in enumerate(gathered):
+                if r == self.rank:
+                    windows[r] = mine.value
+                    continue
+                p = ctypes.c_uint64()
+                ok = ok and lib.b200_peer_window_open(raw, ctypes.byref(p)) == 0
+                windows[r] = p.value
+            ok = ok and lib.b200_peer_setup(self.rank, self.world, windows) == 0
+        agreed = [None] * self.world
+        self.dist.all_gather_object(agreed, ok)
+        if not all(agreed):
+            lib.b200_peer_teardown()
+            return False
+        self.dist.barrier()               # every window is mapped everywhere before the first call
+        self._peer_max = int(lib.b200_peer_max_floats())
+        return True
+
+    def close(self):
+        """Release the peer-memory windows (collective; after the last all-reduce)."""
+        if self._peer_max:
+            from ._lib import lib, check
+            check(lib.b200_sync())
+            self.dist.barrier()
+            self._peer_max = 0
+            check(lib.b200_peer_teardown())
+
+    def _peer_allreduce(self, arr, op):
+        from ._lib import lib, check
+        check(lib.b200_peer_allreduce(arr.ptr, arr.ptr, arr.size, 1 if op == 'avg' else 0))
 
     def _device_stream(self):
         # NCCL work is ordered after, and the library's later kernels after it, by
@@ -61,6 +113,9 @@ class Comm(object):
             return (work, buf if op == 'avg' else None)
         if not arr.is_contiguous:
             raise NotImplementedError('all-reduce of a strided device view')
+        if arr.size <= self._peer_max:
+            self._peer_allreduce(arr, op)     # a kernel on the library stream: nothing to wait for
+            return None
         flat = arr.reshape((arr.size,))
         with torch.cuda.stream(self._device_stream()):
             t = torch.as_tensor(flat, device='cuda')
@@ -106,6 +161,9 @@ class Comm(object):
         if not arr.is_contiguous:
             raise NotImplementedError('all-reduce of a strided device view')
         if arr.size == 0:
+            return
+        if arr.size <= self._peer_max:
+            self._peer_allreduce(arr, op)
             return
         flat = arr.reshape((arr.size,))
         with torch.cuda.stream(self._device_stream()):
@@ -156,7 +214,7 @@ def _element_offset(view, flat):
 OVERLAP_MIN_BYTES = 32 << 20     # gradient vectors below this are all-reduced in one piece
 
 
-def data_parallel(net, comm, axis0_reduce='local', overlap=True):
+def data_parallel(net, comm, axis0_reduce='local', overlap=True, peer=True):
     """Make ``net`` (already on its handler) train data-parallel over ``comm``.
 
     Wraps ``net.backward_pass`` of this instance so that the flat gradient vector
@@ -169,11 +227,17 @@ def data_parallel(net, comm, axis0_reduce='local', overlap=True):
     block of the flat vector, brainstorm/structure/layout.py:149-157), so the
     collective of layer k runs while the layers before it are still computing.
     Networks with gradient modifiers fall back to one all-reduce at the end, since
-    the modifiers run inside the reference's backward_pass (network.py:445)."""
+    the modifiers run inside the reference's backward_pass (network.py:445).
+
+    With ``peer`` (and a ``B200Handler``) all-reduces of small device arrays, i.e. the
+    batch statistics, use the library's kernel over NVLink peer memory instead of a
+    library collective (``Comm.enable_peer``)."""
     handler = net.handler
     if not hasattr(handler, 'set_comm'):
         raise TypeError('handler %r cannot complete sums across ranks' % (handler,))
     handler.set_comm(comm, axis0_reduce)
+    if peer and hasattr(comm, 'enable_peer') and type(handler).__name__ == 'B200Handler':
+        comm.enable_peer()                # small all-reduces over NVLink peer memory, if the node allows it
     local_backward = net.backward_pass
     pending = []
 

@@ -107,6 +107,25 @@ int b200_graph_launch(uint64_t graph);
 int b200_graph_kernel_count(uint64_t graph, uint64_t* kernels);
 int b200_graph_destroy(uint64_t graph);
 
+/* ---- all-reduce of small arrays over NVLink peer memory ---------------------
+ * For the exchanges that sit next to a reduction on this path: the sums over the batch
+ * axis that sum_t(axis=0) completes across batch shards (BatchNorm statistics,
+ * brainstorm/layers/batch_normalization_layer.py:63,117; a few thousand floats).  Every
+ * rank (one process per GPU of one node) allocates a window, exports its handle, opens
+ * the other ranks' handles (exchanged by the host) and registers all of them; one
+ * single-CTA kernel per call then publishes the values, waits (bounded, about a second)
+ * for all ranks and adds the ranks' values in rank order, so every rank gets the same
+ * bits.  Plain peer loads and stores.  Up to 16 ranks, up to b200_peer_max_floats()
+ * floats per call; every rank makes the same calls in the same order.  The reference has
+ * no counterpart (it has no multi-GPU code). */
+uint64_t b200_peer_window_bytes(void);
+int b200_peer_max_floats(void);
+int b200_peer_window_alloc(uint64_t* ptr, void* handle /* 64 bytes */);
+int b200_peer_window_open(const void* handle /* 64 bytes */, uint64_t* ptr);
+int b200_peer_setup(int rank, int world, const uint64_t* windows);
+int b200_peer_allreduce(const float* src, float* dst, int n, int average);
+int b200_peer_teardown(void);
+
 /* ---- CUDA-event timing on the library stream (benchmark support) --------- */
 int b200_event_create(uint64_t* ev);
 int b200_event_record(uint64_t ev);

@@ -27,6 +27,31 @@ def main():
     from brainstorm_b200.workloads import train_steps
     H = B200Handler(seed=3, device=local)
     ok = True
+    # ---- the library's all-reduce over peer memory against NCCL, op by op
+    plain, peer = Comm(), Comm()
+    peer_on = peer.enable_peer()
+    if rank == 0:
+        print('PEER_ON' if peer_on else 'PEER_OFF')
+    if peer_on:
+        rs = np.random.RandomState(100 + rank)
+        for n in (1, 5, 1000, 4096, 65536):
+            for op in ('sum', 'avg'):
+                for rep in range(3):             # repeated calls walk through both slots
+                    x = rs.randn(n).astype(np.float32)
+                    a, b = H.create_from_numpy(x), H.create_from_numpy(x)
+                    plain.allreduce(a, op)
+                    peer.allreduce(b, op)
+                    got, want = H.get_numpy_copy(b), H.get_numpy_copy(a)
+                    gathered = [None] * world
+                    dist.all_gather_object(gathered, got)
+                    same = all(np.array_equal(g, gathered[0]) for g in gathered)
+                    close = np.allclose(got, want, rtol=1e-6, atol=1e-6)
+                    if not (same and close):
+                        ok = False
+                        if rank == 0:
+                            print('peer all-reduce n=%d %s: replicas equal %s, max diff to NCCL %.3g' % (
+                                n, op, same, np.abs(got - want).max()))
+        peer.close()
     for which, build, mode in (
             ('highway_bn', lambda: workloads.highway_bn(batch=32 * world, width=64, classes=7, blocks=2), 'avg'),
             ('lstm', lambda: workloads.lstm(time=6, batch=16 * world, vocab=20, hidden=32), 'local')):

@@ -22,3 +22,5 @@ def test_two_rank_training_matches_global_batch():
                           os.path.join(ROOT, 'tests', 'multi_gpu_worker.py')],
                          capture_output=True, text=True, timeout=600, env=env)
     assert 'MULTI_GPU_OK' in out.stdout, out.stdout[-3000:] + out.stderr[-3000:]
+    # the all-reduce over peer memory must really have been in use on this box
+    assert 'PEER_ON' in out.stdout, out.stdout[-3000:]
