@@ -15,8 +15,8 @@
 //      replicas get the same bits -- and writes the result.
 // Two slots suffice: a rank can only be one epoch ahead of the slowest one, because its
 // next wait needs everybody's next publication, which follows their reads of this epoch.
-// Plain peer loads and stores only; no multimem, no NCCL.  The wait is bounded (about a
-// second); on a timeout the kernel raises the library's device error flag and returns.
+// Plain peer loads and stores only; no multimem, no NCCL.  The wait is bounded (about
+// 20 seconds); on a timeout the kernel raises the library's device error flag and returns.
 //
 // Kernels of different ranks wait for one another, so every rank must run on its own
 // GPU (one process per GPU, as everywhere in this library).
@@ -72,9 +72,11 @@ peer_allreduce_kernel(PeerArgs a, const float* src, float* dst, int n, int avera
     const unsigned long long* counters =
         reinterpret_cast<const unsigned long long*>(a.window[a.rank] + PEER_COUNTER_OFFSET);
     bool seen = false;
-    for (unsigned it = 0; it < (1u << 22) && !seen; ++it) {      // about a second with the back-off below
+    // Ranks drift apart on the host (by seconds while a job starts up), so the bound is
+    // generous: about 20 s (2^22 polls, 4 us apart after the first thousand).
+    for (unsigned it = 0; it < (1u << 22) && !seen; ++it) {
       seen = ld_acquire_sys(counters + threadIdx.x) >= epoch;
-      if (!seen && it > 32) __nanosleep(200);
+      if (!seen && it > 32) __nanosleep(it > 1024 ? 4000 : 200);
     }
     if (!seen) timed_out = 1;
   }
@@ -165,7 +167,7 @@ B200_API int b200_peer_teardown(void) {
 // dst[i] = sum over ranks of src[i] (or the mean), n <= b200_peer_max_floats().  Every rank
 // calls it in the same order with the same n; dst may be src.  Queued on the library's
 // current stream like any other kernel; a rank that never arrives makes the others give up
-// after about a second and raise the device error flag (reported by the next
+// after about 20 seconds and raise the device error flag (reported by the next
 // synchronising call).
 B200_API int b200_peer_allreduce(const float* src, float* dst, int n, int average) {
   if (int rc = require_ready()) return rc;

@@ -113,7 +113,7 @@ int b200_graph_destroy(uint64_t graph);
  * brainstorm/layers/batch_normalization_layer.py:63,117; a few thousand floats).  Every
  * rank (one process per GPU of one node) allocates a window, exports its handle, opens
  * the other ranks' handles (exchanged by the host) and registers all of them; one
- * single-CTA kernel per call then publishes the values, waits (bounded, about a second)
+ * single-CTA kernel per call then publishes the values, waits (bounded, about 20 seconds)
  * for all ranks and adds the ranks' values in rank order, so every rank gets the same
  * bits.  Plain peer loads and stores.  Up to 16 ranks, up to b200_peer_max_floats()
  * floats per call; every rank makes the same calls in the same order.  The reference has
