@@ -214,7 +214,7 @@ def _element_offset(view, flat):
 OVERLAP_MIN_BYTES = 32 << 20     # gradient vectors below this are all-reduced in one piece
 
 
-def data_parallel(net, comm, axis0_reduce='local', overlap=True, peer=True):
+def data_parallel(net, comm, axis0_reduce='local', overlap=True, peer=False):
     """Make ``net`` (already on its handler) train data-parallel over ``comm``.
 
     Wraps ``net.backward_pass`` of this instance so that the flat gradient vector

@@ -61,7 +61,7 @@ def main():
             fuse_lstm_layers(net)
         # one network with an all-reduce per layer (what large networks get), one with a single one
         parallel.OVERLAP_MIN_BYTES = 0 if which == 'highway_bn' else (1 << 40)
-        data_parallel(net, Comm(), axis0_reduce=mode)
+        data_parallel(net, Comm(), axis0_reduce=mode, peer=True)
         losses = train_steps(net, shard_batch(data, rank, world), stepper(), 3)
         params = net.get('parameters')
         gathered = [None] * world
