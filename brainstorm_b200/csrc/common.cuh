@@ -72,9 +72,15 @@ struct State {
   // graph recording (b200_graph_begin .. b200_graph_end)
   bool capturing = false;
   uint64_t* replay_epoch = nullptr;  // device word, advanced before every graph replay
+  int live_graphs = 0;               // recorded graphs that have not been destroyed yet
+  // bounded device waits on another rank (peer all-reduce): polls before the kernel gives up
+  uint32_t peer_spin_limit = 1u << 22;
 };
 State& state();
 int require_ready();
+// Releases a library-owned work buffer that recorded graphs may have baked in: freed at
+// once (stream-ordered) when no recorded graph is alive, else when the last one is destroyed.
+void retire_work_buffer(void* p);
 
 static inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 

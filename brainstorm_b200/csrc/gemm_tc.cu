@@ -939,10 +939,13 @@ int* device_error_flag() {
 // Reports (and clears) a timeout raised by a kernel (a tensor-core GEMM waiting on a
 // barrier, a peer all-reduce waiting for another rank).  Called by the synchronising
 // entry points after the stream has drained.
+void peer_disable();   // peer.cu
+
 int gemm_tc_check_flag() {
   TcHost& h = tc_host();
   if (h.error_flag_host && *h.error_flag_host) {
     *h.error_flag_host = 0;
+    peer_disable();
     return set_error(B200_ERR_DEVICE_FLAG,
                      "a kernel gave up waiting (a tensor-core GEMM on a barrier, or a peer all-reduce on another "
                      "rank); its output is invalid");
@@ -1036,7 +1039,7 @@ static int gemm_tc_impl(int transa, int transb, int64_t M, int64_t N, int64_t K,
       // the buffer outlives the call, so it must not become an allocation of a recorded graph
       B200_REQUIRE(!s.capturing, "the split-K work buffer would have to grow while a graph is being recorded: "
                                  "run the step once before recording it");
-      if (h.partial[si]) B200_CUDA(cudaFreeAsync(h.partial[si], s.stream));
+      retire_work_buffer(h.partial[si]);   // a recorded graph may still replay into the old buffer
       h.partial[si] = nullptr;
       h.partial_bytes[si] = 0;
       B200_CUDA(cudaMallocAsync((void**)&h.partial[si], need, s.stream));

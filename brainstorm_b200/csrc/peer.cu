@@ -16,7 +16,11 @@
 // Two slots suffice: a rank can only be one epoch ahead of the slowest one, because its
 // next wait needs everybody's next publication, which follows their reads of this epoch.
 // Plain peer loads and stores only; no multimem, no NCCL.  The wait is bounded (about
-// 20 seconds); on a timeout the kernel raises the library's device error flag and returns.
+// 20 seconds by default; b200_set_tuning key 8 sets the number of polls); on a timeout the
+// kernel leaves dst untouched, raises the library's device error flag and returns.  The
+// next synchronising call reports the flag and switches the peer path off
+// (b200_peer_enabled() == 0): epochs and slots of the ranks are no longer in step, so
+// callers go back to their library collective until b200_peer_setup is called again.
 //
 // Kernels of different ranks wait for one another, so every rank must run on its own
 // GPU (one process per GPU, as everywhere in this library).
@@ -36,6 +40,7 @@ constexpr size_t PEER_WINDOW_BYTES = PEER_COUNTER_OFFSET + 256;   // counters: P
 
 struct PeerState {
   int rank = -1, world = 0;
+  bool disabled = false;                  // set when a wait ran out (see peer_disable)
   uint8_t* window[PEER_MAX_RANKS] = {};   // [rank] = own window, others = mapped peers
   unsigned long long epoch = 0;           // host copy of the call counter
 } g_peer;
@@ -56,7 +61,7 @@ __device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long
 
 __global__ void __launch_bounds__(1024)
 peer_allreduce_kernel(PeerArgs a, const float* src, float* dst, int n, int average,   // dst may be src
-                      unsigned long long epoch, int* error_flag) {
+                      unsigned long long epoch, int* error_flag, unsigned spin_limit) {
   __shared__ int timed_out;
   const int slot = (int)(epoch & 1);
   float* mine = reinterpret_cast<float*>(a.window[a.rank] + slot * PEER_SLOT_BYTES);
@@ -72,9 +77,9 @@ peer_allreduce_kernel(PeerArgs a, const float* src, float* dst, int n, int avera
     const unsigned long long* counters =
         reinterpret_cast<const unsigned long long*>(a.window[a.rank] + PEER_COUNTER_OFFSET);
     bool seen = false;
-    // Ranks drift apart on the host (by seconds while a job starts up), so the bound is
-    // generous: about 20 s (2^22 polls, 4 us apart after the first thousand).
-    for (unsigned it = 0; it < (1u << 22) && !seen; ++it) {
+    // Ranks drift apart on the host (by seconds while a job starts up), so the default
+    // bound is generous: about 20 s (2^22 polls, 4 us apart after the first thousand).
+    for (unsigned it = 0; it < spin_limit && !seen; ++it) {
       seen = ld_acquire_sys(counters + threadIdx.x) >= epoch;
       if (!seen && it > 32) __nanosleep(it > 1024 ? 4000 : 200);
     }
@@ -95,6 +100,12 @@ peer_allreduce_kernel(PeerArgs a, const float* src, float* dst, int n, int avera
     }
     dst[i] = average ? __fmul_rn(acc, scale) : acc;
   }
+}
+
+// Called by the synchronising entry points when they find the device error flag raised:
+// a peer all-reduce may have given up, after which the ranks' epochs disagree.
+void peer_disable() {
+  if (g_peer.world > 0) g_peer.disabled = true;
 }
 
 }  // namespace b200
@@ -137,17 +148,39 @@ B200_API int b200_peer_window_open(const void* handle, uint64_t* ptr) {
   return B200_OK;
 }
 
+// Gives back a window that never reached b200_peer_setup (a rank whose set-up failed half
+// way): `own` != 0 frees a window of b200_peer_window_alloc, else unmaps one of
+// b200_peer_window_open.
+B200_API int b200_peer_window_release(uint64_t ptr, int own) {
+  if (ptr == 0) return B200_OK;
+  if (own) B200_CUDA(cudaFree((void*)(uintptr_t)ptr));
+  else B200_CUDA(cudaIpcCloseMemHandle((void*)(uintptr_t)ptr));
+  return B200_OK;
+}
+
 // windows[r] for r in [0, world): this rank's own window at [rank], the mapped ones elsewhere.
+// Starts the epochs at zero and clears this rank's arrival counters, so windows that were
+// used before can be registered again.  The host must put a barrier over all ranks between
+// this call and the first b200_peer_allreduce (no rank may publish an epoch into a counter
+// array that is still to be cleared).
 B200_API int b200_peer_setup(int rank, int world, const uint64_t* windows) {
   if (int rc = require_ready()) return rc;
   B200_REQUIRE(world >= 1 && world <= PEER_MAX_RANKS && rank >= 0 && rank < world && windows != nullptr,
                "bad rank / world (at most %d ranks)", PEER_MAX_RANKS);
+  B200_REQUIRE(windows[rank] != 0, "this rank's own window is NULL");
+  B200_CUDA(cudaStreamSynchronize(state().stream));   // calls on an earlier registration have finished
+  B200_CUDA(cudaMemset((uint8_t*)(uintptr_t)windows[rank] + PEER_COUNTER_OFFSET, 0,
+                       PEER_WINDOW_BYTES - PEER_COUNTER_OFFSET));
   g_peer.rank = rank;
   g_peer.world = world;
   g_peer.epoch = 0;
+  g_peer.disabled = false;
   for (int r = 0; r < world; ++r) g_peer.window[r] = (uint8_t*)(uintptr_t)windows[r];
   return B200_OK;
 }
+
+// 1 while b200_peer_allreduce may be used: after b200_peer_setup and until a wait ran out.
+B200_API int b200_peer_enabled(void) { return g_peer.world > 0 && !g_peer.disabled; }
 
 // Unmaps the peers' windows and frees this rank's.  All ranks must have finished their
 // last b200_peer_allreduce (synchronise, then a host barrier) before any rank calls this.
@@ -159,19 +192,24 @@ B200_API int b200_peer_teardown(void) {
     else cudaIpcCloseMemHandle(g_peer.window[r]);
     g_peer.window[r] = nullptr;
   }
+  cudaGetLastError();   // a window that could not be unmapped must not fail the next launch check
   g_peer.world = 0;
   g_peer.rank = -1;
+  g_peer.disabled = false;
   return B200_OK;
 }
 
 // dst[i] = sum over ranks of src[i] (or the mean), n <= b200_peer_max_floats().  Every rank
 // calls it in the same order with the same n; dst may be src.  Queued on the library's
 // current stream like any other kernel; a rank that never arrives makes the others give up
-// after about 20 seconds and raise the device error flag (reported by the next
-// synchronising call).
+// after the poll limit (about 20 seconds by default), leave dst as it was and raise the
+// device error flag: the next synchronising call returns the error and the peer path is
+// off until the next b200_peer_setup.
 B200_API int b200_peer_allreduce(const float* src, float* dst, int n, int average) {
   if (int rc = require_ready()) return rc;
   B200_REQUIRE(g_peer.world > 0, "b200_peer_setup has not been called");
+  B200_REQUIRE(!g_peer.disabled, "the peer all-reduce is switched off: an earlier call gave up waiting for a rank; "
+                                 "register the windows again with b200_peer_setup");
   B200_REQUIRE(n >= 0 && n <= PEER_MAX_FLOATS, "at most %d floats per call", PEER_MAX_FLOATS);
   if (n == 0) return B200_OK;
   B200_REQUIRE(src != nullptr && dst != nullptr, "NULL operand");
@@ -183,7 +221,8 @@ B200_API int b200_peer_allreduce(const float* src, float* dst, int n, int averag
   const unsigned long long epoch = ++g_peer.epoch;
   int threads = (n + 31) / 32 * 32;          // at least one warp (the ranks' counters are handled by threads 0..world-1)
   if (threads > 1024) threads = 1024;
-  peer_allreduce_kernel<<<1, threads, 0, state().stream>>>(a, src, dst, n, average, epoch, device_error_flag());
+  peer_allreduce_kernel<<<1, threads, 0, state().stream>>>(a, src, dst, n, average, epoch, device_error_flag(),
+                                                           state().peer_spin_limit);
   B200_LAUNCH_CHECK();
   return B200_OK;
 }

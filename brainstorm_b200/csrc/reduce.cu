@@ -443,11 +443,12 @@ B200_API int b200_nonfinite_flag(const float* a, int64_t rows, int64_t cols, int
 static __device__ __align__(256) float g_static_sum_scratch[B200_STATIC_SCRATCH_FLOATS];
 
 namespace b200 {
-// In host code the symbol above is only a stand-in, not a device address; the real
-// address is asked for once per device (with that device current) and kept here.
+// In host code the symbol above is only a stand-in, not a device address.  The real
+// address is looked up once per device, with that device current, when b200_init binds
+// the process to its GPU; b200_sum_t_static only reads it here afterwards.
 static float* g_static_scratch_ptr[64] = {nullptr};
 
-static int static_scratch(float** out) {
+int static_scratch_setup() {
   int dev = -1;
   B200_CUDA(cudaGetDevice(&dev));
   B200_REQUIRE(dev >= 0 && dev < 64, "device ordinal %d out of range", dev);
@@ -457,7 +458,6 @@ static int static_scratch(float** out) {
     B200_REQUIRE(p != nullptr, "cudaGetSymbolAddress returned a NULL address");
     g_static_scratch_ptr[dev] = p;
   }
-  *out = g_static_scratch_ptr[dev];
   return B200_OK;
 }
 }  // namespace b200
@@ -466,12 +466,10 @@ B200_API int64_t b200_sum_t_static_max_scratch_floats(void) { return B200_STATIC
 
 // Same result as b200_sum_t (same kernels, same order of additions), but the
 // partial sums go to the library's built-in array: the call allocates nothing.
-// Extents whose partials need more than the array holds are rejected.  The first
-// call on a device looks up the array's device address; make that call before
-// any stream capture begins.  All calls share the one array, which keeps the
-// previous call's partials: nothing in it has to start at zero (pass 1 writes every
-// partial that pass 2 reads), but two such calls that overlap on the GPU (different
-// streams or processes' threads) race on it.
+// Extents whose partials need more than the array holds are rejected.  All calls
+// share the one array, which keeps the previous call's partials: nothing in it has
+// to start at zero (pass 1 writes every partial that pass 2 reads), but two such
+// calls that overlap on the GPU (different streams or processes' threads) race on it.
 B200_API int b200_sum_t_static(const float* a, int64_t rows, int64_t cols, int64_t ld, int axis,
                                float* out) {
   if (int rc = require_ready()) return rc;
@@ -482,7 +480,7 @@ B200_API int b200_sum_t_static(const float* a, int64_t rows, int64_t cols, int64
                "holds %lld: use b200_sum_t with caller-provided scratch",
                (long long)rows, (long long)cols, axis, (long long)need,
                (long long)B200_STATIC_SCRATCH_FLOATS);
-  float* scratch = nullptr;
-  if (int rc = static_scratch(&scratch)) return rc;
+  float* scratch = g_static_scratch_ptr[state().device];
+  B200_REQUIRE(scratch != nullptr, "the built-in scratch array has no address on device %d", state().device);
   return b200_sum_t(a, rows, cols, ld, axis, out, scratch, B200_STATIC_SCRATCH_FLOATS);
 }

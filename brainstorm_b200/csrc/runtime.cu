@@ -5,6 +5,7 @@
 #include <stdarg.h>
 #include <string.h>
 
+#include <unordered_map>
 #include <vector>
 
 #include "common.cuh"
@@ -12,6 +13,7 @@
 namespace b200 {
 
 int gemm_tc_check_flag();  // gemm_tc.cu: reports a barrier timeout of a tensor-core kernel
+int static_scratch_setup();  // reduce.cu: resolves the built-in scratch array of b200_sum_t_static
 
 static thread_local char g_err[512] = "";
 
@@ -48,14 +50,32 @@ namespace {
 struct RecordedGraph {
   cudaGraphExec_t exec = nullptr;
   uint64_t kernels = 0;            // kernel launches recorded (for b200_launch_count)
-  std::vector<void*> owned;        // arrays released by the host during the recording
+  std::vector<void*> owned;        // arrays released by the host that replays still use
+  std::vector<void*> made;         // arrays allocated during the recording
 };
 struct Recording {
   cudaStream_t side_stream = nullptr;
-  std::vector<void*> deferred;
+  std::vector<void*> deferred;     // released by the host during the recording
+  std::vector<void*> made;         // allocated during the recording
   uint64_t launches_at_begin = 0;
 } g_rec;
+// Arrays that were allocated while a graph was being recorded have their addresses baked
+// into it.  The host may keep or drop them as it likes; when it drops one while the graph
+// is alive, the memory stays allocated until the graph is destroyed.
+std::unordered_map<void*, RecordedGraph*> g_made_by;
+// Work buffers of the library (split-K partials) that were replaced while a recorded
+// graph was alive: a replay may still write to them, so they stay allocated until the
+// last graph is gone.
+std::vector<void*> g_retired;
 }  // namespace
+
+namespace b200 {
+void retire_work_buffer(void* p) {
+  if (!p) return;
+  if (state().live_graphs > 0) g_retired.push_back(p);
+  else cudaFreeAsync(p, state().stream);
+}
+}  // namespace b200
 
 B200_API const char* b200_last_error(void) { return g_err; }
 
@@ -88,6 +108,7 @@ B200_API int b200_init(int device) {
   uint64_t keep = UINT64_MAX;
   B200_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
   s.device = device;
+  if (int rc = static_scratch_setup()) return rc;
   s.ready = true;
   return B200_OK;
 }
@@ -114,6 +135,8 @@ B200_API int b200_set_tuning(int key, int value) {
     case 5: s.use_pdl = value ? 1 : 0; break;
     case 7: s.gemm_pair = value ? 1 : 0; break;
     case 6: B200_REQUIRE(value >= 1 && value <= 8, "SM share divisor out of range"); s.sm_share = value; break;
+    case 8: B200_REQUIRE(value >= 0 && value <= 30, "spin limit exponent out of range (0 = default)");
+            s.peer_spin_limit = value ? (1u << value) : (1u << 22); break;
     default: return set_error(B200_ERR_ARG, "unknown tuning key %d", key);
   }
   return B200_OK;
@@ -177,6 +200,7 @@ B200_API int b200_malloc(uint64_t* ptr, uint64_t bytes, int zero) {
     // stream, for real and at once; only the zero fill is recorded.
     B200_CUDA(cudaMallocAsync(&p, n, g_rec.side_stream));
     B200_CUDA(cudaStreamSynchronize(g_rec.side_stream));
+    g_rec.made.push_back(p);
   } else {
     B200_CUDA(cudaMallocAsync(&p, n, state().stream));
   }
@@ -192,6 +216,14 @@ B200_API int b200_free(uint64_t ptr) {
     // stays allocated for as long as the graph exists
     g_rec.deferred.push_back((void*)(uintptr_t)ptr);
     return B200_OK;
+  }
+  if (!g_made_by.empty()) {
+    auto it = g_made_by.find((void*)(uintptr_t)ptr);
+    if (it != g_made_by.end()) {   // replays of that graph still use the address
+      it->second->owned.push_back(it->first);
+      g_made_by.erase(it);
+      return B200_OK;
+    }
   }
   B200_CUDA(cudaFreeAsync((void*)(uintptr_t)ptr, state().stream));
   return B200_OK;
@@ -221,6 +253,7 @@ B200_API int b200_graph_begin(void) {
   B200_CUDA(cudaStreamSynchronize(s.stream));
   if (int rc = gemm_tc_check_flag()) return rc;
   g_rec.deferred.clear();
+  g_rec.made.clear();
   g_rec.launches_at_begin = s.launches;
   B200_CUDA(cudaStreamBeginCapture(s.stream, cudaStreamCaptureModeRelaxed));
   s.capturing = true;
@@ -262,6 +295,10 @@ B200_API int b200_graph_end(uint64_t* graph) {
   r->exec = exec;
   r->kernels = recorded;
   r->owned.swap(g_rec.deferred);
+  r->made.swap(g_rec.made);
+  for (void* p : r->made) g_made_by[p] = r;
+  for (void* p : r->owned) g_made_by.erase(p);    // made and released inside the recording
+  ++s.live_graphs;
   *graph = (uint64_t)(uintptr_t)r;
   return B200_OK;
 }
@@ -288,10 +325,18 @@ B200_API int b200_graph_kernel_count(uint64_t graph, uint64_t* kernels) {
 B200_API int b200_graph_destroy(uint64_t graph) {
   if (graph == 0) return B200_OK;
   RecordedGraph* r = (RecordedGraph*)(uintptr_t)graph;
+  for (void* p : r->made) {
+    auto it = g_made_by.find(p);
+    if (it != g_made_by.end() && it->second == r) g_made_by.erase(it);
+  }
   if (state().ready) {
     // replays still queued use the memory: the frees are ordered after them
     cudaGraphExecDestroy(r->exec);
     release_all(r->owned);
+    if (--state().live_graphs <= 0) {
+      state().live_graphs = 0;
+      release_all(g_retired);
+    }
   }
   delete r;
   return B200_OK;
@@ -375,6 +420,18 @@ B200_API int b200_upload_async(uint64_t dst, const void* src, uint64_t bytes, ui
   if (after_event) B200_CUDA(cudaStreamWaitEvent(g_copy_stream, (cudaEvent_t)(uintptr_t)after_event, 0));
   if (bytes)
     B200_CUDA(cudaMemcpyAsync((void*)(uintptr_t)dst, src, (size_t)bytes, cudaMemcpyHostToDevice, g_copy_stream));
+  return B200_OK;
+}
+
+// The same for a row-pitched destination (a strided view): `rows` rows of `row_bytes` bytes.
+B200_API int b200_upload2d_async(uint64_t dst, uint64_t dst_pitch, const void* src, uint64_t src_pitch,
+                                 uint64_t row_bytes, uint64_t rows, uint64_t after_event) {
+  if (int rc = require_ready()) return rc;
+  B200_NOT_WHILE_RECORDING("an upload");
+  if (int rc = b200_upload_async(0, nullptr, 0, after_event)) return rc;   // stream set-up and ordering
+  if (rows && row_bytes)
+    B200_CUDA(cudaMemcpy2DAsync((void*)(uintptr_t)dst, dst_pitch, src, src_pitch, row_bytes, rows,
+                                cudaMemcpyHostToDevice, g_copy_stream));
   return B200_OK;
 }
 

@@ -46,10 +46,12 @@ class RecordedStep(object):
 
     Arrays that the recorded calls touch must stay alive for as long as the step is
     replayed; arrays released *during* the recording are kept alive by the
-    recording itself."""
+    recording itself, and so are the work arrays the handler and the fused layers
+    lent to the recorded calls (``keep``)."""
 
-    def __init__(self, handle):
+    def __init__(self, handle, keep=()):
         self._handle = int(handle)
+        self._keep = list(keep)
         n = ctypes.c_uint64()
         check(lib.b200_graph_kernel_count(self._handle, ctypes.byref(n)))
         self.kernels = int(n.value)
@@ -65,12 +67,26 @@ class RecordedStep(object):
         handle, self._handle = self._handle, 0
         if handle:
             check(lib.b200_graph_destroy(handle))
+        self._keep = []
 
     def __del__(self):
         try:
             self.release()
         except Exception:  # interpreter shutdown
             pass
+
+
+def _release_handover_slots():
+    """The fused LSTM layers leave work arrays for the layer that is called next
+    (fused_lstm._handover).  Emptied while a recording is still open, the arrays are
+    released inside it, and the library keeps such memory until the recording is
+    destroyed; left in place, the next ordinary pass would free memory that every
+    replay still writes."""
+    import sys
+    mod = sys.modules.get('brainstorm_b200.fused_lstm')
+    if mod is not None:
+        for k in mod._handover:
+            mod._handover[k] = None
 
 
 def record(fn, *args, **kwargs):
@@ -80,16 +96,27 @@ def record(fn, *args, **kwargs):
     Calls that wait for the device or cross PCIe (``get_numpy_copy``,
     ``set_from_numpy``, ``synchronize`` ...) raise ``B200Error`` and the recording
     is discarded.  Run ``fn`` once the ordinary way first: work buffers that grow on
-    first use cannot grow inside a recording."""
+    first use cannot grow inside a recording.
+
+    ``handler`` (keyword, optional): the handler whose calls are recorded.  Its
+    reduction scratch array is baked into the recording, so the recording keeps a
+    reference to it: a later ordinary ``sum_t`` that needs a larger one allocates a
+    new array without freeing the one replays still use."""
+    handler = kwargs.pop('handler', None)
     check(lib.b200_graph_begin())
     try:
         fn(*args, **kwargs)
+        _release_handover_slots()
     except BaseException:
         lib.b200_graph_end(None)   # discard; the original exception is the one to report
         raise
     handle = ctypes.c_uint64()
     check(lib.b200_graph_end(ctypes.byref(handle)))
-    return RecordedStep(handle.value)
+    keep = []
+    scratch = getattr(handler, '_scratch', None)
+    if scratch is not None:
+        keep.append(scratch)
+    return RecordedStep(handle.value, keep)
 
 
 def _scalars(obj):
@@ -145,5 +172,5 @@ class GraphedStepper(_StepperBase):
             if self._eager_left > 0:
                 self._eager_left -= 1
                 return self.stepper.run()
-            self._step = record(self.stepper.run)
+            self._step = record(self.stepper.run, handler=self.net.handler)
         self._step.launch()

@@ -173,14 +173,20 @@ class B200Handler(Handler):
 
     def upload_async(self, mem, arr, after_event=0):
         """Start copying the page-locked float32 array ``arr`` (see pinned_empty)
-        into the contiguous device array ``mem`` on the upload stream, after the
-        event ``after_event`` (record_event) if given.  Kernels queued after
-        ``upload_join()`` see the data."""
+        into the device array ``mem`` (contiguous or row-pitched) on the upload
+        stream, after the event ``after_event`` (record_event) if given.  Kernels
+        queued after ``upload_join()`` see the data."""
         arr = np.asarray(arr)
-        if arr.dtype != _f32 or not arr.flags.c_contiguous or arr.size != mem.size or not mem._contig:
-            raise ValueError('upload_async needs a contiguous float32 source of the same size '
-                             'and a contiguous destination')
-        check(lib.b200_upload_async(mem.ptr, arr.ctypes.data, arr.nbytes, after_event))
+        if arr.dtype != _f32 or not arr.flags.c_contiguous or arr.size != mem.size:
+            raise ValueError('upload_async needs a contiguous float32 source of the same size')
+        if mem._contig:
+            check(lib.b200_upload_async(mem.ptr, arr.ctypes.data, arr.nbytes, after_event))
+            return
+        form = mem.as_2d()
+        if form is None:
+            raise NotImplementedError('view with strides %r has no row-pitched form' % (mem.strides,))
+        rows, cols, ld = form
+        check(lib.b200_upload2d_async(mem.ptr, ld * 4, arr.ctypes.data, cols * 4, cols * 4, rows, after_event))
 
     def upload_join(self):
         check(lib.b200_upload_join())
@@ -222,6 +228,7 @@ class B200Handler(Handler):
         them; returns a ``RecordedStep`` whose ``launch()`` replays them with one
         call (see ``brainstorm_b200.graph``)."""
         from .graph import record
+        kwargs['handler'] = self
         return record(fn, *args, **kwargs)
 
     def synchronize(self):
@@ -334,14 +341,22 @@ class B200Handler(Handler):
 
     def broadcast_t(self, a, axis, out):
         assert (out.shape[:axis] + (1,) + out.shape[axis + 1:]) == a.shape
-        if not (a._contig and out._contig):
-            raise NotImplementedError('broadcast_t needs contiguous operands')
+        if out.size == 0:
+            return
+        if not a._contig:
+            a = self._contiguous_copy(a)
+        if not out._contig:
+            # a strided view (a feature slice of a hub with several sources,
+            # buffer_structure.py:232-245): broadcast into a contiguous temporary,
+            # then one row-pitched copy
+            tmp = B200Array.empty(out.shape, zero=False)
+            self.broadcast_t(a, axis, tmp)
+            self.copy_to(tmp, out)
+            return
         # out viewed as (outer, n_axis, inner); a as (outer, 1, inner)
         outer = int(np.prod(out.shape[:axis], dtype=np.int64))
         n_axis = out.shape[axis]
         inner = int(np.prod(out.shape[axis + 1:], dtype=np.int64))
-        if out.size == 0:
-            return
         if outer == 1:
             check(lib.b200_broadcast_t(a.ptr, out.ptr, n_axis, inner, inner, 0))
         elif inner == 1:
@@ -430,19 +445,29 @@ class B200Handler(Handler):
     # ----------------------------------------------------------- concat / split
     def merge_tt(self, a, b, out):
         assert a.shape[-1] + b.shape[-1] == out.shape[-1]
-        if not (a._contig and b._contig and out._contig):
-            raise NotImplementedError('merge_tt needs contiguous operands')
         na, nb = a.shape[-1], b.shape[-1]
-        rows = out.size // (na + nb) if na + nb else 0
-        check(lib.b200_merge_tt(a.ptr, b.ptr, out.ptr, rows, na, nb))
+        if a._contig and b._contig and out._contig:
+            rows = out.size // (na + nb) if na + nb else 0
+            check(lib.b200_merge_tt(a.ptr, b.ptr, out.ptr, rows, na, nb))
+            return
+        # strided views: two row-pitched copies into the two column ranges of out
+        if na and a.size:
+            self.copy_to(a, out[..., :na])
+        if nb and b.size:
+            self.copy_to(b, out[..., na:])
 
     def split_add_tt(self, x, out_a, out_b):
         assert out_a.shape[-1] + out_b.shape[-1] == x.shape[-1]
-        if not (x._contig and out_a._contig and out_b._contig):
-            raise NotImplementedError('split_add_tt needs contiguous operands')
         na, nb = out_a.shape[-1], out_b.shape[-1]
-        rows = x.size // (na + nb) if na + nb else 0
-        check(lib.b200_split_add_tt(x.ptr, out_a.ptr, out_b.ptr, rows, na, nb))
+        if x._contig and out_a._contig and out_b._contig:
+            rows = x.size // (na + nb) if na + nb else 0
+            check(lib.b200_split_add_tt(x.ptr, out_a.ptr, out_b.ptr, rows, na, nb))
+            return
+        # strided views: two row-pitched accumulations from the two column ranges of x
+        if na and out_a.size:
+            self.add_tt(out_a, x[..., :na], out_a)
+        if nb and out_b.size:
+            self.add_tt(out_b, x[..., na:], out_b)
 
     # ------------------------------------------------------------------- labels
     def binarize_v(self, v, out):

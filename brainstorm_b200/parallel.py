@@ -37,6 +37,7 @@ class Comm(object):
         self.rank = dist.get_rank()
         self._stream = None
         self._peer_max = 0        # > 0: device arrays up to this many floats go over peer memory
+        self._peer_windows = False   # this Comm registered peer windows that close() must release
 
     def enable_peer(self):
         """Set up the library's all-reduce over NVLink peer memory for small device
@@ -47,7 +48,7 @@ class Comm(object):
         everything on NCCL, if any rank cannot set it up."""
         import ctypes
         from ._lib import lib
-        if self.world == 1 or self._peer_max:
+        if self.world == 1 or (self._peer_max and lib.b200_peer_enabled()):
             return bool(self._peer_max)
         if self.world > 16:
             return False
@@ -62,32 +63,58 @@ class Comm(object):
         self.dist.all_gather_object(gathered, (ok, handle.raw if ok else None))
         ok = all(g[0] for g in gathered)
         windows = (ctypes.c_uint64 * self.world)()
+        opened = []
+        registered = False
         if ok:
             for r, (_, raw) in enumerate(gathered):
                 if r == self.rank:
                     windows[r] = mine.value
                     continue
                 p = ctypes.c_uint64()
-                ok = ok and lib.b200_peer_window_open(raw, ctypes.byref(p)) == 0
+                if lib.b200_peer_window_open(raw, ctypes.byref(p)) != 0:
+                    ok = False
+                    break
+                opened.append(p.value)
                 windows[r] = p.value
-            ok = ok and lib.b200_peer_setup(self.rank, self.world, windows) == 0
+            if ok:
+                registered = ok = lib.b200_peer_setup(self.rank, self.world, windows) == 0
         agreed = [None] * self.world
         self.dist.all_gather_object(agreed, ok)
         if not all(agreed):
-            lib.b200_peer_teardown()
+            if registered:
+                lib.b200_peer_teardown()          # frees this rank's window and unmaps the others
+            else:                                 # never registered: give the pieces back one by one
+                for p in opened:
+                    lib.b200_peer_window_release(p, 0)
+                lib.b200_peer_window_release(mine.value, 1)
             return False
-        self.dist.barrier()               # every window is mapped everywhere before the first call
+        self.dist.barrier()               # every window is mapped and cleared everywhere before the first call
         self._peer_max = int(lib.b200_peer_max_floats())
+        self._peer_windows = True
         return True
 
     def close(self):
         """Release the peer-memory windows (collective; after the last all-reduce)."""
-        if self._peer_max:
+        if self._peer_windows:
             from ._lib import lib, check
-            check(lib.b200_sync())
+            lib.b200_sync()               # an error flagged earlier has been reported already
             self.dist.barrier()
             self._peer_max = 0
+            self._peer_windows = False
             check(lib.b200_peer_teardown())
+
+    def _peer_ok(self, arr):
+        """True if ``arr`` goes over peer memory.  After a wait ran out (a rank never
+        arrived; the library reported it at a synchronising call) the ranks' call counters
+        no longer agree and the library has switched the path off: everything goes back to
+        NCCL until ``enable_peer`` is called again."""
+        if not self._peer_max or arr.size > self._peer_max:
+            return False
+        from ._lib import lib
+        if not lib.b200_peer_enabled():
+            self._peer_max = 0
+            return False
+        return True
 
     def _peer_allreduce(self, arr, op):
         from ._lib import lib, check
@@ -116,8 +143,8 @@ class Comm(object):
             work = self.dist.all_reduce(torch.from_numpy(buf), op=self.dist.ReduceOp.SUM, async_op=True)
             return (work, buf if op == 'avg' else None)
         if not arr.is_contiguous:
-            raise NotImplementedError('all-reduce of a strided device view')
-        if arr.size <= self._peer_max:
+            raise NotImplementedError('asynchronous all-reduce of a strided device view')
+        if self._peer_ok(arr):
             self._peer_allreduce(arr, op)     # a kernel on the library stream: nothing to wait for
             return None
         flat = arr.reshape((arr.size,))
@@ -162,11 +189,16 @@ class Comm(object):
             if op == 'avg':
                 buf /= buf.dtype.type(self.world)
             return
-        if not arr.is_contiguous:
-            raise NotImplementedError('all-reduce of a strided device view')
         if arr.size == 0:
             return
-        if arr.size <= self._peer_max:
+        if not arr.is_contiguous:           # a strided view: through a contiguous temporary
+            from .handler import _any_handler
+            h = _any_handler()
+            tmp = h._contiguous_copy(arr)
+            self.allreduce(tmp, op)
+            h.copy_to(tmp, arr)
+            return
+        if self._peer_ok(arr):
             self._peer_allreduce(arr, op)
             return
         flat = arr.reshape((arr.size,))
@@ -239,6 +271,12 @@ def data_parallel(net, comm, axis0_reduce='local', overlap=True, peer=False):
     handler = net.handler
     if not hasattr(handler, 'set_comm'):
         raise TypeError('handler %r cannot complete sums across ranks' % (handler,))
+    if axis0_reduce == 'sum':
+        # every sum over the batch axis would be summed over the ranks, the bias and BatchNorm
+        # gradients among them, and the gradient average that follows would leave those `world`
+        # times too large next to the weight gradients
+        raise ValueError("axis0_reduce='sum' is for plain op sequences (the op-suite benchmark); "
+                         "training needs 'avg' (global batch statistics) or 'local'")
     handler.set_comm(comm, axis0_reduce)
     if peer and hasattr(comm, 'enable_peer') and type(handler).__name__ == 'B200Handler':
         comm.enable_peer()                # small all-reduces over NVLink peer memory, if the node allows it

@@ -20,6 +20,41 @@ def _bs():
     return bs
 
 
+def op_suite_inputs(rows, cols, seed, alloc=None):
+    """Inputs of the handler op suite: fp32 (rows, cols) operands ``a``, ``b``, ``dy``
+    uniform[-4, 4], a (1, cols) row vector, a (rows, 1) column vector, divisors ``div``
+    uniform[0.5, 4] with a random sign, and int32 ``labels`` uniform in [0, cols), all
+    from ``RandomState(seed)``.  The draw runs in row blocks (a few hundred MB of
+    float64 at a time), which consumes the generator's stream exactly as one draw per
+    array would; ``alloc(shape)`` may supply the float32 arrays (e.g. page-locked)."""
+    rs = np.random.RandomState(seed)
+    f32 = np.float32
+    alloc = alloc or (lambda shape: np.empty(shape, f32))
+    block = max(1, (1 << 25) // max(cols, 1))          # rows per block: 32 Mi samples
+
+    def u(shape, lo=-4.0, hi=4.0, out=None):
+        out = alloc(shape) if out is None else out
+        for r0 in range(0, shape[0], block):
+            r1 = min(shape[0], r0 + block)
+            out[r0:r1] = rs.random_sample((r1 - r0,) + tuple(shape[1:])).astype(f32) * f32(hi - lo) + f32(lo)
+        return out
+
+    d = {}
+    d['a'] = u((rows, cols))
+    d['b'] = u((rows, cols))
+    d['dy'] = u((rows, cols))
+    d['row'] = u((1, cols))
+    d['col'] = u((rows, 1))
+    sign = np.empty((rows, cols), f32)
+    for r0 in range(0, rows, block):
+        r1 = min(rows, r0 + block)
+        sign[r0:r1] = np.where(rs.random_sample((r1 - r0, cols)) < 0.5, f32(-1), f32(1))
+    d['div'] = u((rows, cols), 0.5, 4.0)
+    d['div'] *= sign
+    d['labels'] = rs.randint(0, cols, size=(rows, 1)).astype(np.int32)
+    return d
+
+
 def mlp(batch=100, hidden=1200, n_in=784, n_out=10, seed=42, data_seed=0):
     bs = _bs()
     bs.global_rnd.set_seed(seed)

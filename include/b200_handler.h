@@ -42,7 +42,9 @@ int b200_device_info(int* device, int* sm_count, uint64_t* free_bytes, uint64_t*
  * 5: programmatic dependent launch inside the LSTM time loops (default 1);
  * 6: split-K plans for 1/value of the SMs (default 1; 2 while two streams share the GPU);
  * 7: 256-wide GEMM tiles on pairs of SMs (tcgen05 cta_group::2; default 0: measured slower
- *    than the single-SM tiles so far). */
+ *    than the single-SM tiles so far);
+ * 8: the bounded wait of the peer all-reduce gives up after 2^value polls (0 = the default,
+ *    2^22 polls, about 20 seconds). */
 int b200_set_tuning(int key, int value);
 uint64_t b200_stream(void);                            /* the main stream (a cudaStream_t) */
 /* A second compute stream, for work that may run beside the main stream's (a stack of
@@ -87,6 +89,8 @@ int b200_memcpy2d_d2h(void* dst, uint64_t dst_pitch, uint64_t src, uint64_t src_
  * queued on the compute stream afterwards wait for all uploads issued so far.  The
  * host source must be page-locked and stay untouched until then. */
 int b200_upload_async(uint64_t dst, const void* src, uint64_t bytes, uint64_t after_event);
+int b200_upload2d_async(uint64_t dst, uint64_t dst_pitch, const void* src, uint64_t src_pitch,
+                        uint64_t row_bytes, uint64_t rows, uint64_t after_event);   /* row-pitched destination */
 int b200_upload_join(void);
 
 /* ---- recorded steps: one replay call instead of one launch per kernel -------
@@ -98,8 +102,10 @@ int b200_upload_join(void);
  * scalar arguments are frozen in the recording; random masks are not: every replay
  * draws from a new Philox stream.  While recording, calls that wait for the device
  * or cross PCIe (transfers, uploads, b200_sync, events) fail with an error and
- * record nothing; arrays allocated are real allocations; arrays released stay
- * allocated until b200_graph_destroy.  b200_graph_end(NULL) discards the recording.
+ * record nothing; arrays allocated are real allocations; arrays released while
+ * recording, and arrays that were allocated while recording and are released later,
+ * stay allocated until b200_graph_destroy (replays keep using their addresses), and so
+ * do the library's own work buffers.  b200_graph_end(NULL) discards the recording.
  * The reference has no counterpart (its GPU backend launches kernel by kernel). */
 int b200_graph_begin(void);                                               /* synchronises */
 int b200_graph_end(uint64_t* graph);
@@ -113,16 +119,24 @@ int b200_graph_destroy(uint64_t graph);
  * brainstorm/layers/batch_normalization_layer.py:63,117; a few thousand floats).  Every
  * rank (one process per GPU of one node) allocates a window, exports its handle, opens
  * the other ranks' handles (exchanged by the host) and registers all of them; one
- * single-CTA kernel per call then publishes the values, waits (bounded, about 20 seconds)
- * for all ranks and adds the ranks' values in rank order, so every rank gets the same
- * bits.  Plain peer loads and stores.  Up to 16 ranks, up to b200_peer_max_floats()
- * floats per call; every rank makes the same calls in the same order.  The reference has
+ * single-CTA kernel per call then publishes the values, waits (bounded, about 20 seconds;
+ * b200_set_tuning key 8) for all ranks and adds the ranks' values in rank order, so every
+ * rank gets the same bits.  Plain peer loads and stores.  Up to 16 ranks, up to
+ * b200_peer_max_floats() floats per call; every rank makes the same calls in the same
+ * order.  A wait that runs out leaves dst untouched and raises the device error flag: the
+ * next synchronising call fails, and b200_peer_enabled() is 0 until the windows are
+ * registered again (the ranks' call counters no longer agree).  b200_peer_setup clears this
+ * rank's arrival counters: put a host barrier over all ranks between it and the first
+ * b200_peer_allreduce.  b200_peer_window_release gives back a window that never reached
+ * b200_peer_setup (own != 0: allocated here; 0: opened from a handle).  The reference has
  * no counterpart (it has no multi-GPU code). */
 uint64_t b200_peer_window_bytes(void);
 int b200_peer_max_floats(void);
 int b200_peer_window_alloc(uint64_t* ptr, void* handle /* 64 bytes */);
 int b200_peer_window_open(const void* handle /* 64 bytes */, uint64_t* ptr);
+int b200_peer_window_release(uint64_t ptr, int own);
 int b200_peer_setup(int rank, int world, const uint64_t* windows);
+int b200_peer_enabled(void);
 int b200_peer_allreduce(const float* src, float* dst, int n, int average);
 int b200_peer_teardown(void);
 
@@ -212,7 +226,8 @@ int b200_index_m_by_v(const float* m, int64_t ldm, const float* v, int64_t ldv, 
  *      axis 0: out[c] = sum_r a[r,c]; axis 1: out[r] = sum_c a[r,c]; axis -1:
  *      out[0] = sum of everything.  Sums are deterministic two-pass trees; the
  *      caller provides the scratch for the partials (size from
- *      b200_sum_t_scratch_floats, which depends on the extents only). -------- */
+ *      b200_sum_t_scratch_floats, which depends on the extents and on the number of
+ *      SMs of the GPU the process was bound to, never on the pointers). ------- */
 int64_t b200_sum_t_scratch_floats(int64_t rows, int64_t cols, int64_t ld, int axis);
 int b200_sum_t(const float* a, int64_t rows, int64_t cols, int64_t ld, int axis, float* out, float* scratch, int64_t scratch_floats);
 /* No counterpart in the reference.  sum_t for hosts that may not allocate device
@@ -220,8 +235,8 @@ int b200_sum_t(const float* a, int64_t rows, int64_t cols, int64_t ld, int axis,
  * enter the CUDA allocator): the partial sums go to a 1 MiB array built into the
  * library instead of caller scratch; the call allocates nothing.  Same result as
  * b200_sum_t.  Extents that need more than b200_sum_t_static_max_scratch_floats()
- * are rejected.  The first call on a device resolves the array's address: make it
- * before any stream capture.  Calls share the array; overlapping calls race. */
+ * are rejected.  b200_init resolves the array's device address, once per device.
+ * Calls share the array; calls that overlap on the GPU race. */
 int64_t b200_sum_t_static_max_scratch_floats(void);
 int b200_sum_t_static(const float* a, int64_t rows, int64_t cols, int64_t ld, int axis, float* out);
 int b200_softmax_m(const float* m, float* out, int64_t rows, int64_t cols, int64_t ldm, int64_t ldo);

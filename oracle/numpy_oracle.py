@@ -293,25 +293,10 @@ class OracleHandler(object):
 # the same data).
 # --------------------------------------------------------------------------
 def op_suite_inputs(rows, cols, seed):
-    """Inputs of the handler op suite: fp32 (rows, cols) uniform[-4, 4]
-    operands, a (1, cols) row vector, a (rows, 1) column vector, divisors
-    uniform[0.5, 4] with a random sign and int labels uniform in [0, cols)."""
-    rs = np.random.RandomState(seed)
-    f32 = np.float32
-
-    def u(shape, lo=-4.0, hi=4.0):
-        return (rs.random_sample(shape).astype(f32) * f32(hi - lo) + f32(lo))
-
-    d = {}
-    d['a'] = u((rows, cols))
-    d['b'] = u((rows, cols))
-    d['dy'] = u((rows, cols))
-    d['row'] = u((1, cols))
-    d['col'] = u((rows, 1))
-    sign = np.where(rs.random_sample((rows, cols)) < 0.5, f32(-1), f32(1))
-    d['div'] = (u((rows, cols), 0.5, 4.0) * sign).astype(f32)
-    d['labels'] = rs.randint(0, cols, size=(rows, 1)).astype(np.int32)
-    return d
+    """Inputs of the handler op suite (the workload's own seeded generator; the
+    checker and the checked side must see the same arrays)."""
+    from brainstorm_b200.workloads import op_suite_inputs as make
+    return make(rows, cols, seed)
 
 
 # --------------------------------------------------------------------------

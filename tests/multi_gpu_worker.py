@@ -1,4 +1,5 @@
-"""Worker of tests/test_multi_gpu.py: one rank per GPU (torch.distributed.run).
+"""Worker of tests/test_multi_gpu.py: one rank per GPU (torch.distributed.run), on as many
+GPUs as the box shows (2, 4 or 8).
 Each rank trains on its batch shard with B200Handler + data_parallel; rank 0 checks
 the result against the single-process run of the reference stack on NumpyHandler
 with the whole batch."""

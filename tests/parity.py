@@ -68,7 +68,7 @@ def reduction_scale(op, arrays, kwargs, call):
             s = s + np.abs(arrays['out'])
         return s
     if op == 'softmax_m':
-        return 1.0
+        return 0.0          # every term of the denominator is positive: a pure relative bound
     if op.startswith(('conv2d', 'avgpool2d', 'maxpool2d')):
         # sums of a few dozen terms of order one: one scale for all outputs
         return float(max(np.abs(v).max() for v in arrays.values() if v.size) *
@@ -78,3 +78,56 @@ def reduction_scale(op, arrays, kwargs, call):
 
 REDUCTION_OPS = {'sum_t', 'dot_mm', 'dot_add_mm', 'softmax_m', 'conv2d_forward_batch', 'conv2d_backward_batch',
                  'avgpool2d_forward_batch', 'avgpool2d_backward_batch', 'maxpool2d_backward_batch'}
+
+
+def lstm_term_scales(params, x, y, internals, out_deltas, y_context=None, ca_context=None):
+    """Per-element error scales of every buffer the LSTM layer fills
+    (brainstorm/layers/lstm_layer.py:106-278), from one CPU run's own values.
+
+    A buffer element that is a sum gets the sum of the absolute values of its terms; an
+    element that is a product or a slope-<=1 function of such sums gets the scale of the
+    sum times the other factor.  All arrays cover the T time steps of the pass (context
+    slot stripped); ``params`` maps the fifteen parameter names to arrays.  Returns
+    {buffer name: scale array}, with 'y', 'dx' and 'grad.<name>' beside the internals."""
+    A = lambda v: np.abs(np.asarray(v, dtype=np.float32))
+    P = {k: A(v) for k, v in params.items()}
+    T, B, H = y.shape
+    x2 = A(x).reshape(T * B, -1)
+    ya = A(y)
+    y0 = np.zeros_like(ya[:1]) if y_context is None else A(y_context).reshape(1, B, H)
+    y_prev = np.concatenate([y0, ya[:-1]]).reshape(T * B, H)
+    I = {k: A(v) for k, v in internals.items()}
+    ca = I['Ca']
+    c0 = np.zeros_like(ca[:1]) if ca_context is None else A(ca_context).reshape(1, B, H)
+    ca_prev = np.concatenate([c0, ca[:-1]])
+    pi, pf, po = (P[k].reshape(1, 1, H) for k in ('pi', 'pf', 'po'))
+    S = {}
+    # forward (:117-145): the four pre-activations, then the cell and the output
+    pre = {g: (x2 @ P['W' + g].T + y_prev @ P['R' + g].T).reshape(T, B, H) + P['b' + g].reshape(1, 1, H)
+           for g in 'zifo'}
+    pre['i'] = pre['i'] + ca_prev * pi
+    pre['f'] = pre['f'] + ca_prev * pf
+    pre['o'] = pre['o'] + ca * po
+    for g in 'zifo':
+        S[g.upper() + 'a'] = S[g.upper() + 'b'] = pre[g]
+    S['Ca'] = S['Cb'] = I['Ib'] * I['Zb'] + I['Fb'] * ca_prev + pre['z'] + pre['i'] + pre['f'] * ca_prev
+    S['y'] = S['Ca'] + pre['o']
+    # backward (:171-205): dy = output deltas + sum over gates of dG[t+1].R; the cell delta adds five terms
+    nxt = lambda a: np.concatenate([a[1:], np.zeros_like(a[:1])])
+    dG = {g: I['d%sa' % g.upper()] for g in 'zifo'}
+    s_dy = A(out_deltas) + sum(nxt(dG[g]).reshape(T * B, H) @ P['R' + g] for g in 'zifo').reshape(T, B, H)
+    s_dca = nxt(dG['i']) * pi + nxt(dG['f']) * pf + dG['o'] * po + I['dCb'] + nxt(I['dCa']) * nxt(I['Fb'])
+    s_bwd = (s_dy * (1 + ca) + s_dca) * (1 + ca_prev)
+    for k in ('dZa', 'dZb', 'dIa', 'dIb', 'dFa', 'dFb', 'dOa', 'dOb', 'dCa', 'dCb'):
+        S[k] = s_bwd
+    # input deltas (:216-219) and gradients (:221-278)
+    dGf = {g: dG[g].reshape(T * B, H) for g in 'zifo'}
+    S['dx'] = sum(dGf[g] @ P['W' + g] for g in 'zifo').reshape(np.shape(x))
+    for g in 'zifo':
+        S['grad.W' + g] = dGf[g].T @ x2
+        S['grad.R' + g] = dGf[g].T @ y_prev
+        S['grad.b' + g] = dGf[g].sum(0)
+    extra = (ca[-1:] * dG['i'][:1]).sum((0, 1))        # the term of :272-278
+    for name, g, c in (('pi', 'i', ca_prev), ('pf', 'f', ca_prev), ('po', 'o', ca)):
+        S['grad.' + name] = ((c * dG[g]).sum((0, 1)) + extra).reshape(1, H)
+    return S

@@ -139,3 +139,59 @@ def test_strided_views_on_device():
     got = H.get_numpy_copy(dev)
     parity.assert_elementwise_close(got, big)
     parity.assert_bits_equal(got[:, :, 9], big[:, :, 9])
+
+
+@pytest.mark.gpu
+def test_merge_split_broadcast_on_feature_slices():
+    """merge_tt / split_add_tt / broadcast_t on the row-pitched views that a hub with
+    several sources hands out (buffer[:, :, f0:f1], buffer_structure.py:232-245),
+    against the same numpy expressions NumpyHandler uses (numpy_handler.py:221,251,103)."""
+    from brainstorm_b200 import B200Handler
+    import parity
+    H = B200Handler(rng_mode='host', seed=1)
+    rs = np.random.RandomState(8)
+    T, B = 5, 7
+    hub = rs.randn(T, B, 20).astype(np.float32)
+    dev = H.create_from_numpy(hub)
+    # merge: two strided sources into a strided destination of a second hub
+    hub2 = rs.randn(T, B, 16).astype(np.float32)
+    dev2 = H.create_from_numpy(hub2)
+    H.merge_tt(dev[:, :, 2:7], dev[:, :, 11:15], dev2[:, :, 3:12])
+    hub2[:, :, 3:12] = np.concatenate((hub[:, :, 2:7], hub[:, :, 11:15]), axis=-1)
+    parity.assert_bits_equal(H.get_numpy_copy(dev2), hub2, 'merge_tt strided')
+    # merge: contiguous sources, strided destination, and the other way round
+    a, b = rs.randn(T, B, 4).astype(np.float32), rs.randn(T, B, 3).astype(np.float32)
+    H.merge_tt(H.create_from_numpy(a), H.create_from_numpy(b), dev2[:, :, 0:7])
+    hub2[:, :, 0:7] = np.concatenate((a, b), axis=-1)
+    parity.assert_bits_equal(H.get_numpy_copy(dev2), hub2, 'merge_tt into a slice')
+    out = H.zeros((T, B, 9))
+    H.merge_tt(dev[:, :, 0:4], dev[:, :, 4:9], out)
+    parity.assert_bits_equal(H.get_numpy_copy(out), hub[:, :, 0:9], 'merge_tt from slices')
+    # split_add: accumulates the two column ranges of x into two strided outputs
+    x = rs.randn(T, B, 9).astype(np.float32)
+    H.split_add_tt(H.create_from_numpy(x), dev[:, :, 1:5], dev[:, :, 10:15])
+    hub[:, :, 1:5] += x[:, :, :4]
+    hub[:, :, 10:15] += x[:, :, 4:]
+    parity.assert_elementwise_close(H.get_numpy_copy(dev), hub, 'split_add_tt')
+    xs = dev2[:, :, 2:11]
+    oa, ob = H.ones((T, B, 4)), H.ones((T, B, 5))
+    H.split_add_tt(xs, oa, ob)
+    parity.assert_elementwise_close(H.get_numpy_copy(oa), 1 + hub2[:, :, 2:6], 'split_add_tt')
+    parity.assert_elementwise_close(H.get_numpy_copy(ob), 1 + hub2[:, :, 6:11], 'split_add_tt')
+    # broadcast along time, batch and features into a strided destination
+    for axis, shape in ((0, (1, B, 6)), (1, (T, 1, 6)), (2, (T, B, 1))):
+        src = rs.randn(*shape).astype(np.float32)
+        H.broadcast_t(H.create_from_numpy(src), axis, dev[:, :, 8:14])
+        hub[:, :, 8:14] = np.broadcast_to(src, (T, B, 6))
+        parity.assert_bits_equal(H.get_numpy_copy(dev), hub, 'broadcast_t axis %d' % axis)
+    # a strided source
+    H.broadcast_t(dev2[:, :, 5:6], 2, dev[:, :, 0:3])
+    hub[:, :, 0:3] = np.broadcast_to(hub2[:, :, 5:6], (T, B, 3))
+    parity.assert_bits_equal(H.get_numpy_copy(dev), hub, 'broadcast_t from a slice')
+    # uploads into a slice on the upload stream
+    part = H.pinned_empty((T, B, 5))
+    part[...] = rs.randn(T, B, 5)
+    H.upload_async(dev[:, :, 15:20], part)
+    H.upload_join()
+    hub[:, :, 15:20] = part
+    parity.assert_bits_equal(H.get_numpy_copy(dev), hub, 'upload_async into a slice')

@@ -156,6 +156,30 @@ def test_highway_batchnorm_stack():
     _check_training(workloads.highway_bn, steps=2, rtol=2e-4, batch=96, width=64, classes=10, blocks=3)
 
 
+def _two_sources(batch=6, time=3, n_in=12, n_out=5, seed=42, data_seed=0):
+    """Two layers feeding one input: their outputs (and output deltas) are feature
+    slices of one hub, i.e. row-pitched views (buffer_structure.py:232-245)."""
+    import brainstorm as bs
+    bs.global_rnd.set_seed(seed)
+    inp, fc = bs.tools.get_in_out_layers('classification', (n_in,), n_out)
+    inp >> bs.layers.FullyConnected(7, name='A', activation='tanh') >> fc
+    inp >> bs.layers.FullyConnected(9, name='B', activation='sigmoid') >> fc
+    net = bs.Network.from_layer(fc)
+    net.initialize(bs.initializers.Gaussian(0.1))
+    rs = np.random.RandomState(data_seed)
+    data = {'default': rs.randn(time, batch, n_in).astype(np.float32),
+            'targets': rs.randint(0, n_out, (time, batch, 1)).astype(np.int32)}
+    return net, data, lambda: bs.training.SgdStepper(learning_rate=0.1)
+
+
+def test_hub_with_two_sources_hands_out_strided_views():
+    net_cpu, net_gpu = _check_training(_two_sources, steps=3, rtol=2e-5)
+    assert not net_gpu.buffer['A'].outputs.default.is_contiguous
+    assert not net_gpu.buffer['B'].output_deltas.default.is_contiguous
+    for path in ('A.outputs.default', 'B.outputs.default', 'A.output_deltas.default', 'B.output_deltas.default'):
+        _close(net_gpu.get(path), net_cpu.get(path), 2e-5, path)
+
+
 def test_handler_is_describable_and_weight_modifier_runs():
     import brainstorm as bs
     from brainstorm.describable import get_description, create_from_description

@@ -68,12 +68,14 @@ def test_fused_lstm_entry_points_match_reference_layer(tag):
     check(lib.b200_lstm_forward(xproj.ptr, Rst.ptr, bst.ptr, pst.ptr, *[f[k].ptr for k in no.LSTM_FORWARD],
                                 f['y'].ptr, y_work.ptr, r_work.ptr, T, B, Hs, 1))
 
-    def close(got, want, what):
-        scale = np.abs(want).max() + 1e-30
-        assert np.abs(got - want).max() <= 2e-5 * scale, (what, np.abs(got - want).max(), scale)
+    internals = {k: v[:T] for k, v in list(f_ref.items()) + list(d_ref.items()) if k != 'y'}
+    S = parity.lstm_term_scales(p, x, f_ref['y'][:T], internals, deltas[:T])
+
+    def close(got, want, scale, what):      # element by element, scale = sum of |terms| of that element
+        parity.assert_reduction_close(got, want, scale, 'lstm', what)
 
     for k in f:
-        close(H_.get_numpy_copy(f[k])[:T], f_ref[k][:T], k)
+        close(H_.get_numpy_copy(f[k])[:T], f_ref[k][:T], S[k], k)
     d = {k: H_.zeros((T + 1, B, Hs)) for k in d_ref}
     dG = H_.zeros((T + 1, B, 4 * Hs))
     order = ('dZa', 'dZb', 'dIa', 'dIb', 'dFa', 'dFb', 'dOa', 'dOb', 'dCa', 'dCb')
@@ -82,10 +84,11 @@ def test_fused_lstm_entry_points_match_reference_layer(tag):
                                  f['Ob'].ptr, f['Ca'].ptr, f['Cb'].ptr, *[d[k].ptr for k in order],
                                  dG.ptr, r_work.ptr, T, B, Hs, 1))
     for k in d:
-        close(H_.get_numpy_copy(d[k])[:T], d_ref[k][:T], k)
+        close(H_.get_numpy_copy(d[k])[:T], d_ref[k][:T], S[k], k)
     stacked = np.concatenate([d_ref[k][:T] for k in ('dZa', 'dIa', 'dFa', 'dOa')], axis=2)
-    close(H_.get_numpy_copy(dG)[:T], stacked, 'stacked gate deltas')
+    close(H_.get_numpy_copy(dG)[:T], stacked, np.concatenate([S['dZa']] * 4, axis=2), 'stacked gate deltas')
     # weight gradients from the stacked deltas, as the fused layer computes them
     dW = H_.zeros((4 * Hs, n_in))
     H_.dot_add_mm(dG[:T].reshape((T * B, 4 * Hs)), dx_flat, dW, transa=True)
-    close(H_.get_numpy_copy(dW), np.concatenate([g_ref['Wz'], g_ref['Wi'], g_ref['Wf'], g_ref['Wo']], axis=0), 'dW')
+    close(H_.get_numpy_copy(dW), np.concatenate([g_ref['Wz'], g_ref['Wi'], g_ref['Wf'], g_ref['Wo']], axis=0),
+          np.concatenate([S['grad.W' + g] for g in 'zifo'], axis=0), 'dW')

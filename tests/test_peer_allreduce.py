@@ -33,3 +33,45 @@ def test_single_rank_all_reduce_is_the_identity_through_both_slots():
     finally:
         H.synchronize()
         check(lib.b200_peer_teardown())
+
+
+def test_a_rank_that_never_arrives_makes_the_wait_run_out_and_is_reported():
+    """Failure detection without a fault: "rank 1" is a second window of this process
+    that nobody ever publishes to, and the wait's poll limit is set to a few
+    milliseconds.  The kernel must return by itself, leave dst alone, raise the device
+    error flag (reported by the next synchronising call) and switch the peer path off;
+    ordinary calls keep working and a new registration brings the path back."""
+    from brainstorm_b200 import B200Handler, B200Error
+    from brainstorm_b200._lib import lib, check
+    H = B200Handler(seed=1)
+    handles = [ctypes.create_string_buffer(64) for _ in range(2)]
+    wins = [ctypes.c_uint64() for _ in range(2)]
+    for w, h in zip(wins, handles):
+        check(lib.b200_peer_window_alloc(ctypes.byref(w), h))
+    windows = (ctypes.c_uint64 * 2)(wins[0].value, wins[1].value)
+    check(lib.b200_peer_setup(0, 2, windows))
+    check(lib.b200_set_tuning(8, 12))                 # 2^12 polls: about 12 ms
+    try:
+        assert lib.b200_peer_enabled() == 1
+        x = np.arange(1000, dtype=np.float32)
+        src, dst = H.create_from_numpy(x), H.ones((1000,))
+        H.synchronize()
+        check(lib.b200_peer_allreduce(src.ptr, dst.ptr, 1000, 0))     # queued; rank 1 never comes
+        with pytest.raises(B200Error, match='gave up waiting'):
+            H.synchronize()
+        assert lib.b200_peer_enabled() == 0
+        assert np.all(H.get_numpy_copy(dst) == 1.0)                   # flag cleared, dst untouched
+        assert lib.b200_peer_allreduce(src.ptr, dst.ptr, 1000, 0) != 0
+        assert b'switched off' in lib.b200_last_error()
+        H.add_tt(src, src, dst)                                       # the library is still usable
+        assert np.array_equal(H.get_numpy_copy(dst), 2 * x)
+        # registering again (alone this time) clears the counters and brings the path back
+        check(lib.b200_peer_setup(0, 1, (ctypes.c_uint64 * 1)(wins[0].value)))
+        assert lib.b200_peer_enabled() == 1
+        check(lib.b200_peer_allreduce(src.ptr, dst.ptr, 1000, 0))
+        assert np.array_equal(H.get_numpy_copy(dst), x)
+    finally:
+        check(lib.b200_set_tuning(8, 0))              # back to the default limit
+        lib.b200_sync()
+        check(lib.b200_peer_teardown())               # frees window 0 (this rank's)
+        check(lib.b200_peer_window_release(wins[1].value, 1))

@@ -286,6 +286,54 @@ def test_reference_trainer_runs_on_a_graphed_stepper():
     assert np.array_equal(results[0][1], results[1][1])
 
 
+@pytest.mark.gpu
+@needs_reference
+def test_eager_work_between_replays_does_not_pull_memory_from_under_the_recording():
+    """A recording bakes in the addresses of work arrays it did not get from the caller: the
+    split-K partials of the GEMMs, the handler's reduction scratch, the arrays one fused
+    LSTM layer hands to the next.  A Trainer with a validation monitor runs ordinary
+    forward passes between replays, and any other ordinary call may need a larger work
+    array.  None of that may free memory a replay still writes."""
+    from brainstorm_b200 import B200Handler, GraphedStepper, workloads
+    from brainstorm_b200.fused_lstm import fuse_lstm_layers
+    kw = dict(time=64, batch=16, vocab=20, hidden=32)      # 64 timesteps: two pieces, so layers hand work arrays over
+    results = []
+    for wrap in (lambda s: s, GraphedStepper):
+        net, data, stepper = workloads.lstm(**kw)
+        H = B200Handler(seed=3)
+        net.set_handler(H)
+        fuse_lstm_layers(net)
+        st = wrap(stepper())
+        st.start(net)
+        rs = np.random.RandomState(9)
+        big_a = H.create_from_numpy(rs.randn(128, 4096).astype(np.float32))
+        big_b = H.create_from_numpy(rs.randn(256, 4096).astype(np.float32))
+        tall = H.create_from_numpy(rs.randn(4096, 3000).astype(np.float32))
+        losses = []
+        for i in range(6):
+            batch = {k: np.roll(v, i, axis=1) for k, v in data.items()}
+            net.provide_external_data(batch)
+            st.run()
+            losses.append(float(net.get_loss_values()['total_loss']))
+            if i == 2:        # steps 1 and 2 were the recording and its first replay
+                net.forward_pass(training_pass=False)          # takes and drops the handed-over arrays
+                out = H.zeros((128, 256))
+                H.dot_mm(big_a, big_b, out, transb=True)       # split-K: a much larger partial buffer
+                col = H.zeros((1, 3000))
+                H.sum_t(tall, 0, col)                          # needs more scratch than the step did
+                junk = [H.allocate((1 << 18,)) for _ in range(24)]
+                for j in junk:                                 # whatever was freed is reused and poisoned
+                    H.fill(j, float('nan'))
+                H.synchronize()
+                del junk
+        results.append((net.get('parameters'), losses))
+        if wrap is GraphedStepper:
+            assert st._step is not None and len(st._step._keep) >= 1
+    assert results[0][1] == results[1][1]
+    assert np.isfinite(results[1][0]).all()
+    assert np.array_equal(results[0][0], results[1][0])
+
+
 # ------------------------------------------------------------------ GraphedStepper logic, no GPU
 class _FakeStep(object):
     def __init__(self):
@@ -331,6 +379,7 @@ def _graphed(monkeypatch):
     made = []
 
     def fake_record(fn, *a, **k):
+        k.pop('handler', None)           # whose work arrays the recording keeps alive
         fn(*a, **k)                      # a recording runs the calls once (without executing them)
         made.append(_FakeStep())
         return made[-1]

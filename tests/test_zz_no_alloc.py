@@ -49,3 +49,24 @@ def test_static_scratch_rejects_oversize_and_does_not_touch_out():
     msg = lib.b200_last_error().decode()
     assert 'built-in array' in msg and 'b200_sum_t' in msg
     assert (H.get_numpy_copy(out) == 1).all()
+
+
+def test_static_scratch_sum_of_a_row_pitched_view():
+    """Sum over everything of a view whose rows are 520 floats apart but 515 long: the
+    row sums and the partials of their sum share the built-in array."""
+    H, lib, check = _abi()
+    rows, cols, ld = 3000, 515, 520
+    rs = np.random.RandomState(11)
+    need = lib.b200_sum_t_scratch_floats(rows, cols, ld, -1)
+    assert 0 < need <= lib.b200_sum_t_static_max_scratch_floats()
+    scratch = H.allocate((int(need),))
+    for call in range(2):
+        full = rs.uniform(-4, 4, (rows, ld)).astype(np.float32)
+        d = H.create_from_numpy(full)
+        want, got = H.zeros((1,)), H.zeros((1,))
+        check(lib.b200_sum_t(d.ptr, rows, cols, ld, -1, want.ptr, scratch.ptr, scratch.size))
+        check(lib.b200_sum_t_static(d.ptr, rows, cols, ld, -1, got.ptr))
+        w, g = H.get_numpy_copy(want), H.get_numpy_copy(got)
+        a = full[:, :cols].astype(np.float64)
+        assert np.array_equal(g, w)
+        assert abs(float(g[0]) - a.sum()) <= 1e-5 * np.abs(a).sum()
