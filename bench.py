@@ -100,26 +100,12 @@ def make_suite(H, t):
 
 
 def host_inputs(rows, cols, seed, alloc=None):
-    """Seeded synthetic operands.  A (rows/16, cols) block is drawn from the seeded
-    generator and tiled down the rows: the value distribution is the workload's
-    (uniform[-4, 4]; divisors uniform[0.5, 4] with a random sign; labels uniform in
-    [0, cols)) and generating 4 GiB of random numbers does not dominate start-up."""
-    from oracle.numpy_oracle import op_suite_inputs
-    block_rows = max(rows // 16, 1)
-    blk = op_suite_inputs(block_rows, cols, seed)
-    reps = -(-rows // block_rows)
-    alloc = alloc or (lambda shape: np.empty(shape, np.float32))
-    d = {}
-    for k in ('a', 'b', 'dy', 'div'):
-        full = alloc((rows, cols))
-        for r in range(reps):
-            lo = r * block_rows
-            hi = min(rows, lo + block_rows)
-            full[lo:hi] = blk[k][:hi - lo]
-        d[k] = full
-    d['row'] = blk['row']
-    d['col'] = np.tile(blk['col'], (reps, 1))[:rows].copy()
-    d['labels'] = np.tile(blk['labels'], (reps, 1))[:rows].astype(np.float32)
+    """The workload's seeded synthetic operands: the full draw of
+    ``workloads.op_suite_inputs`` (uniform[-4, 4]; divisors uniform[0.5, 4] with a random
+    sign; labels uniform in [0, cols)), labels as the fp32 column the handler takes."""
+    from brainstorm_b200.workloads import op_suite_inputs
+    d = op_suite_inputs(rows, cols, seed, alloc=alloc)
+    d['labels'] = d['labels'].astype(np.float32)
     return d
 
 
@@ -196,7 +182,7 @@ def cpu_suite_time(rows, cols, seed, threads, steps, warmup):
     over `threads` host threads (numpy releases the GIL).  Returns GB/s, seconds per
     step and the kind of handler used."""
     from concurrent.futures import ThreadPoolExecutor
-    from oracle.numpy_oracle import op_suite_inputs
+    from brainstorm_b200.workloads import op_suite_inputs
     O, kind = cpu_handler()
     d = op_suite_inputs(rows, cols, seed)
     labels = d['labels'].astype(np.float32)
@@ -307,145 +293,138 @@ def run_reference(args):
     print(json.dumps(line))
 
 
-# ------------------------------------------------------------------ LSTM training step
-def lstm_training(H, world, rank, steps, barrier, lib, check):
-    """Second half of the metric: training sequences per second of the character
-    LSTM (time 100, batch 128 per GPU, 205 symbols, 2 x 1000 units, SoftmaxCE, SGD),
-    run through the reference's unchanged Network / SgdStepper on this handler with
-    the fused LSTM layer.  Every step uploads its batch from host memory and reads
-    the loss back, as Trainer does."""
+# ------------------------------------------------------------------ training workloads
+def _reference_on_path():
     ref = os.path.join(ROOT, 'baseline', '_ref')
     if os.path.isdir(os.path.join(ref, 'brainstorm')) and ref not in sys.path:
         sys.path.insert(0, ref)
     try:
         import brainstorm  # noqa: F401
+        return None
     except Exception as e:
-        return {'unavailable': 'brainstorm (the caller of the handler) is not importable: %s' % e}
+        return 'brainstorm (the caller of the handler) is not importable: %s' % e
+
+
+def _max_over_ranks(value, world):
+    if world == 1:
+        return value
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([value], device='cuda', dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def _timed_steps(step, steps, barrier, world, warm=3):
+    """ms per step: host wall clock around `steps` whole updates (each ends with the loss
+    read-back), bracketed by a barrier and a synchronisation, max over ranks."""
+    for _ in range(warm):
+        loss = step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        loss = step()
+    barrier()
+    return _max_over_ranks((time.perf_counter() - t0) / steps, world) * 1e3, loss
+
+
+def lstm_training(H, world, rank, steps, barrier, lib):
+    """Second half of the metric: training sequences per second of the character LSTM
+    (time 100, batch 128 per GPU, 205 symbols, 2 x 1000 units, SoftmaxCE, SGD) through the
+    reference's unchanged Network / SgdStepper on this handler with the fused LSTM layer
+    and 16-byte aligned hubs.  Every step uploads its batch from page-locked host memory
+    and reads the loss back, as Trainer does.  Timed twice: every rank on its own (the
+    one-GPU figure, no exchange), then data-parallel with the gradient all-reduce."""
+    why = _reference_on_path()
+    if why:
+        return {'unavailable': why}
     from brainstorm_b200 import workloads
     from brainstorm_b200.fused_lstm import fuse_lstm_layers
+    from brainstorm_b200.layout import align_buffers
+    from brainstorm_b200.pipeline import PrefetchingIterator, defer_loss_readback
     T, B = 100, 128
     net, data, stepper = workloads.lstm(time=T, batch=B, data_seed=rank)
     pinned = {}
-    for k, v in data.items():                     # host batches live in page-locked memory
+    for k, v in data.items():
         pinned[k] = H.pinned_empty(v.shape, np.float32)
         pinned[k][...] = v
-    data = pinned
     net.set_handler(H)
     fuse_lstm_layers(net)
+    align_buffers(net)
+    st = stepper()
+    st.start(net)
+
+    def step():
+        net.provide_external_data(pinned)
+        st.run()
+        return float(net.get_loss_values()['total_loss'])
+
+    out = {'T': T, 'batch_per_gpu': B, 'global_batch': world * B, 'hidden': 1000, 'layers': 2, 'steps': steps}
+    ms1, loss = _timed_steps(step, steps, barrier, 1)
+    out['n1_ms'] = round(ms1, 3)
+    out['n1_sequences_per_s'] = round(B / ms1 * 1e3, 1)
+    ms = ms1
     if world > 1:
         from brainstorm_b200.parallel import Comm, data_parallel
         data_parallel(net, Comm())
-    st = stepper()
-    st.start(net)
-
-    def step():
-        net.provide_external_data(data)
-        st.run()
-        return float(net.get_loss_values()['total_loss'])
-
-    for _ in range(3):
-        loss = step()
-    barrier()
-    l0 = lib.b200_launch_count()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        loss = step()
-    barrier()
-    dt = (time.perf_counter() - t0) / steps
-    if world > 1:
-        import torch
-        import torch.distributed as dist
-        tt = torch.tensor([dt], device='cuda')
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        dt = float(tt.item())
-    return {'sequences_per_s': round(world * B / dt, 1), 'ms_per_step': round(dt * 1e3, 3),
-            'time_steps': T, 'batch_per_gpu': B, 'global_batch': world * B, 'hidden': 1000, 'layers': 2,
-            'steps': steps, 'loss': round(loss, 4),
-            'gpu_launches_per_step': int((lib.b200_launch_count() - l0) // steps),
-            'h2d_bytes_per_step': int(sum(v.nbytes for v in data.values())),
-            'timing': 'host wall clock around whole steps (each step ends with the loss read-back), max over ranks',
-            'parallelism': 'dp%d, gradient all-reduce (avg) of %d parameters' % (world, net.buffer.parameters.size)}
-
-
-def other_training_configs(H, rank, lib, only=None):
-    """Single-GPU step times of the two other training workloads (extra keys of
-    the bench line): the MNIST-style MLP (batch 100, momentum SGD) and the Highway +
-    BatchNorm stack (batch 8192, width 4096, 10 blocks)."""
-    try:
-        import brainstorm  # noqa: F401
-    except Exception as e:
-        return {'unavailable': 'brainstorm is not importable: %s' % e}
-    from brainstorm_b200 import workloads
-    out = {}
-    for name, build, steps in (('mlp', workloads.mlp, 50), ('highway_bn', workloads.highway_bn, 3)):
-        if only and name != only:
-            continue
-        net, data, stepper = build()
-        net.set_handler(H)
-        st = stepper()
-        st.start(net)
-
-        def step():
-            net.provide_external_data(data)
-            st.run()
-            return float(net.get_loss_values()['total_loss'])
-
-        for _ in range(3):
-            step()
-        H.synchronize()
         l0 = lib.b200_launch_count()
-        t0 = time.perf_counter()
-        for _ in range(steps):
-            step()
-        H.synchronize()
-        dt = (time.perf_counter() - t0) / steps
-        batch = data['default'].shape[1]
-        out[name] = {'samples_per_s': round(batch / dt, 1), 'ms_per_step': round(dt * 1e3, 3), 'batch': batch,
-                     'gpu_launches_per_step': int((lib.b200_launch_count() - l0) // steps)}
-        if name == 'mlp':
-            # the same step replayed from a recording (one launch call per step)
-            from brainstorm_b200 import GraphedStepper
-            st = GraphedStepper(stepper(), eager_steps=1)
-            st.start(net)
-            for _ in range(3):
-                step()
-            H.synchronize()
+        ms, loss = _timed_steps(step, steps, barrier, world)
+        out['launches_per_step'] = int((lib.b200_launch_count() - l0) // (steps + 3))
+        out['allreduce_floats'] = int(net.buffer.parameters.size)
+    out['ms_per_step'] = round(ms, 3)
+    out['sequences_per_s'] = round(world * B / ms * 1e3, 1)
+    out['vs_n1'] = round(out['sequences_per_s'] / out['n1_sequences_per_s'], 3)
+    out['loss'] = round(loss, 4)
+    # the same updates with the next batch uploaded during the step and the loss read one call late
+    import brainstorm as bs
+    n = steps + 3
+    many = {k: np.concatenate([v] * n, axis=1) for k, v in data.items()}
+    it = PrefetchingIterator(bs.data_iterators.Minibatches(B, shuffle=False, **many))
+    deferred = defer_loss_readback(net)
+    barrier()
+    t0, k = None, 0
+    for batch in it(handler=H):
+        if k == 3:
+            barrier()
             t0 = time.perf_counter()
-            for _ in range(steps):
-                step()
-            H.synchronize()
-            dt = (time.perf_counter() - t0) / steps
-            out[name]['recorded_ms_per_step'] = round(dt * 1e3, 3)
-            out[name]['recorded_samples_per_s'] = round(batch / dt, 1)
-            st.invalidate()
-        del net
+        net.provide_external_data(batch)
+        st.run()
+        net.get_loss_values()
+        k += 1
+    deferred.flush()
+    barrier()
+    out['pipelined_ms'] = round(_max_over_ranks((time.perf_counter() - t0) / (k - 3), world) * 1e3, 3)
+    deferred.restore()
+    out['h2d_bytes_per_step'] = int(sum(v.nbytes for v in pinned.values()))
     return out
 
 
-def sharded_training(name, H, world, rank, barrier, lib):
-    """The two other training workloads on `world` GPUs.  'highway_bn': the Highway +
-    BatchNorm stack with its batch of 8192 sharded over the ranks (strong scaling, 8192 /
-    world rows per GPU); BatchNorm batch statistics are completed across the shards inside
-    ``sum_t(axis=0)`` (NCCL, 16 KiB each).  'mlp': the MNIST-style MLP with 100 samples per
-    GPU (weak scaling).  Gradients are all-reduced per layer in both."""
-    try:
-        import brainstorm  # noqa: F401
-    except Exception as e:
-        return {'unavailable': 'brainstorm is not importable: %s' % e}
-    import torch
-    import torch.distributed as dist
-    from brainstorm_b200 import workloads
-    from brainstorm_b200.parallel import Comm, data_parallel
-    if name == 'highway_bn':
-        global_batch, steps, scaling = 8192, 3, 'strong'
-        net, data, stepper = workloads.highway_bn(batch=global_batch // world, data_seed=rank)
-        reduce_mode = 'avg'
-    else:
-        global_batch, steps, scaling = 100 * world, 50, 'weak'
+def other_training(name, H, world, rank, barrier, lib, new_event, elapsed):
+    """The two other training workloads.  'mlp': the MNIST-style MLP, batch 100 per GPU
+    (weak scaling), momentum SGD.  'highway_bn': ten Highway + BatchNorm blocks of width
+    4096, batch 8192 in total (strong scaling: 8192 / N rows per GPU), BatchNorm statistics
+    completed across the shards inside sum_t(axis=0).  Plain stepper and the same step
+    replayed from a recording; at N > 1 the Highway step also reports its phases."""
+    why = _reference_on_path()
+    if why:
+        return {'unavailable': why}
+    from brainstorm_b200 import GraphedStepper, workloads
+    from brainstorm_b200.layout import align_buffers
+    if name == 'mlp':
         net, data, stepper = workloads.mlp(batch=100, data_seed=rank)
-        reduce_mode = 'local'
+        global_batch, steps, mode = 100 * world, 50, 'local'
+    else:
+        net, data, stepper = workloads.highway_bn(batch=8192 // world, data_seed=rank)
+        global_batch, steps, mode = 8192, 3 if world == 1 else 6, 'avg'
     net.set_handler(H)
-    data_parallel(net, Comm(), axis0_reduce=reduce_mode)
+    align_buffers(net)
+    phase_events = {}
+    if world > 1:
+        from brainstorm_b200.parallel import Comm, data_parallel
+        comm = Comm()
+        mark = (lambda tag: phase_events.__setitem__(tag, H.record_event(phase_events.get(tag)))) \
+            if name == 'highway_bn' else None
+        data_parallel(net, comm, axis0_reduce=mode, peer=(name == 'highway_bn'), on_phase=mark)
     st = stepper()
     st.start(net)
 
@@ -454,24 +433,93 @@ def sharded_training(name, H, world, rank, barrier, lib):
         st.run()
         return float(net.get_loss_values()['total_loss'])
 
-    for _ in range(3):
-        step()
-    barrier()
     l0 = lib.b200_launch_count()
-    t0 = time.perf_counter()
-    for _ in range(steps):
+    ms, _ = _timed_steps(step, steps, barrier, world)
+    out = {'samples_per_s': round(global_batch / ms * 1e3, 1), 'ms_per_step': round(ms, 3), 'global_batch': global_batch,
+           'launches_per_step': int((lib.b200_launch_count() - l0) // (steps + 3))}
+    if phase_events:
+        # one more step with the phases bracketed by events on the library stream
+        fwd0 = net.forward_pass
+
+        def forward_pass(*a, **k):
+            mark('start')
+            fwd0(*a, **k)
+            mark('forward_done')
+        net.forward_pass = forward_pass
         step()
-    barrier()
-    tt = torch.tensor([(time.perf_counter() - t0) / steps], device='cuda')
-    dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-    dt = float(tt.item())
-    return {'samples_per_s': round(global_batch / dt, 1), 'ms_per_step': round(dt * 1e3, 3), 'global_batch': global_batch,
-            'batch_per_gpu': global_batch // world, 'scaling': scaling,
-            'gpu_launches_per_step': int((lib.b200_launch_count() - l0) // steps),
-            'parallelism': 'dp%d: gradient all-reduce (avg) of %d parameters, %s%s' % (
-                world, net.buffer.parameters.size, 'per layer' if name == 'highway_bn' else 'in one piece',
-                ', BatchNorm statistics all-reduced (avg) inside sum_t(axis=0)' if name == 'highway_bn' else ''),
-            'timing': 'host wall clock around whole steps, max over ranks'}
+        mark('updated')
+        net.forward_pass = fwd0
+        H.synchronize()
+        order = ['start', 'forward_done', 'backward_queued', 'reduced', 'updated']
+        names = ['forward', 'backward', 'allreduce_tail', 'update']
+        out['phases_ms'] = {n: round(_max_over_ranks(elapsed(phase_events[a], phase_events[b]), world), 3)
+                            for n, a, b in zip(names, order[:-1], order[1:])}
+        # time the host needs to queue one step (no waiting): a step cannot be shorter than this
+        H.synchronize()
+        t0 = time.perf_counter()
+        net.provide_external_data(data)
+        st.run()
+        out['host_queue_ms'] = round(_max_over_ranks((time.perf_counter() - t0), world) * 1e3, 3)
+        H.synchronize()
+    if name == 'mlp' or world > 1:
+        gs = GraphedStepper(stepper(), eager_steps=1)
+        gs.start(net)
+        st = gs
+        ms, _ = _timed_steps(step, steps, barrier, world)
+        if gs._step is not None:
+            out['recorded_ms_per_step'] = round(ms, 3)
+            out['recorded_samples_per_s'] = round(global_batch / ms * 1e3, 1)
+        gs.invalidate()
+    return out
+
+
+# ------------------------------------------------------------------ GEMM block
+GEMM_CASES = [('NT', 8192, 4096, 4096, False, True), ('NN', 8192, 4096, 4096, False, False),
+              ('TN', 8192, 4096, 4096, True, False), ('NT_step', 128, 4000, 1000, False, True)]
+
+
+def gemm_block(H, lib, check, new_event, elapsed, local_rank, peaks):
+    """dot_mm on the tensor cores at the shapes of the training workloads: one call timed on
+    its own and 400 calls back to back (the power cap then sets the clock), with the SM
+    clock seen during the loop.  frac = TFLOP/s over a third of half the measured bf16
+    rate (TF32 runs at half the bf16 rate; three TF32 products per fp32 product)."""
+    rs = np.random.RandomState(7)
+    out = {}
+    burst = float(peaks.get('bf16_tflops', 1590.0)) / 6.0
+    sustained = float(peaks.get('bf16_tflops_sustained', 1400.0)) / 6.0
+    for name, M, N, K, ta, tb in GEMM_CASES:
+        a = H.create_from_numpy(rs.uniform(-1, 1, (K, M) if ta else (M, K)).astype(np.float32))
+        b = H.create_from_numpy(rs.uniform(-1, 1, (N, K) if tb else (K, N)).astype(np.float32))
+        c = H.zeros((M, N))
+        for _ in range(3):
+            H.dot_mm(a, b, c, transa=ta, transb=tb)
+        single = []
+        e0, e1 = new_event(), new_event()
+        for _ in range(5):
+            H.synchronize()
+            time.sleep(0.02)
+            check(lib.b200_event_record(e0))
+            H.dot_mm(a, b, c, transa=ta, transb=tb)
+            check(lib.b200_event_record(e1))
+            single.append(elapsed(e0, e1))
+        reps = 400 if M * N * K > 1e9 else 2000
+        sampler = ClockSampler(local_rank)
+        H.synchronize()
+        t0 = time.time()
+        check(lib.b200_event_record(e0))
+        for _ in range(reps):
+            H.dot_mm(a, b, c, transa=ta, transb=tb)
+        check(lib.b200_event_record(e1))
+        loop_ms = elapsed(e0, e1) / reps
+        clk = sampler.stop(t0, time.time())
+        flop = 2.0 * M * N * K
+        tf1, tfl = flop / min(single) / 1e9, flop / loop_ms / 1e9
+        out[name] = {'mnk': [M, N, K], 'single_tflops': round(tf1, 1), 'loop_tflops': round(tfl, 1),
+                     'frac_burst': round(tf1 / burst, 3), 'frac_sustained': round(tfl / sustained, 3),
+                     'loop_sm_mhz': clk.get('sm_mhz'), 'us': round(min(single) * 1e3, 1)}
+        del a, b, c
+    out['peak_tflops'] = {'burst': round(burst, 1), 'sustained': round(sustained, 1)}
+    return out
 
 
 # ------------------------------------------------------------------ GPU arm
@@ -491,6 +539,13 @@ def run_b200(args):
     if world > 1:
         dist.init_process_group('nccl', device_id=torch.device('cuda', local_rank))
     H = B200Handler(seed=SEED + rank, device=local_rank)
+    peaks, peak_src = {}, 'fallback'
+    try:
+        with open(os.path.join(ROOT, 'MEASURED_PEAKS.json')) as f:
+            peaks = json.load(f)
+        peak, peak_src = float(peaks['hbm_gbs']), 'measured'
+    except Exception:
+        peak = 6650.0
 
     def barrier():
         check(lib.b200_sync())
@@ -508,34 +563,26 @@ def run_b200(args):
         check(lib.b200_event_elapsed_ms(e0, e1, ctypes.byref(ms)))
         return ms.value
 
+    def finish(line):
+        if rank == 0:
+            print(json.dumps(line))
+        if world > 1:
+            barrier()
+            dist.destroy_process_group()
+
     if args.only == 'gemm':
         return run_gemm(args, H, lib, check, new_event, elapsed)
+    if args.only == 'gemms':
+        return finish({'metric': 'dot_mm_fp32_tflops', 'n_gpus': world,
+                       'gemm': gemm_block(H, lib, check, new_event, elapsed, local_rank, peaks)})
     if args.only in ('mlp', 'highway_bn'):
-        ref = os.path.join(ROOT, 'baseline', '_ref')
-        if os.path.isdir(os.path.join(ref, 'brainstorm')) and ref not in sys.path:
-            sys.path.insert(0, ref)
-        if world > 1:
-            res = {args.only: sharded_training(args.only, H, world, rank, barrier, lib)}
-            if rank == 0:
-                print(json.dumps({'metric': '%s_train_samples_per_s' % args.only,
-                                  'value': res[args.only].get('samples_per_s'), 'unit': 'samples/s',
-                                  'n_gpus': world, 'detail': res}))
-            dist.destroy_process_group()
-            return
-        res = other_training_configs(H, rank, lib, only=args.only)
-        if rank == 0:
-            print(json.dumps({'metric': '%s_train_samples_per_s' % args.only,
-                              'value': res.get(args.only, {}).get('samples_per_s'), 'unit': 'samples/s',
-                              'n_gpus': world, 'detail': res}))
-        return
+        res = other_training(args.only, H, world, rank, barrier, lib, new_event, elapsed)
+        return finish({'metric': '%s_train_samples_per_s' % args.only, 'value': res.get('samples_per_s'),
+                       'unit': 'samples/s', 'n_gpus': world, 'detail': res})
     if args.only == 'lstm':
-        lstm = lstm_training(H, world, rank, max(1, args.steps), barrier, lib, check)
-        if rank == 0:
-            print(json.dumps({'metric': 'lstm_train_sequences_per_s', 'value': lstm.get('sequences_per_s'),
-                              'unit': 'sequences/s', 'n_gpus': world, 'lstm': lstm}))
-        if world > 1:
-            dist.destroy_process_group()
-        return
+        lstm = lstm_training(H, world, rank, max(1, args.steps), barrier, lib)
+        return finish({'metric': 'lstm_train_sequences_per_s', 'value': lstm.get('sequences_per_s'),
+                       'unit': 'sequences/s', 'n_gpus': world, 'lstm': lstm})
     ROWS = args.rows
     # ---- operands: page-locked host copies (for e2e) and device-resident arrays
     host = host_inputs(ROWS, COLS, SEED + rank, alloc=H.pinned_empty)
@@ -553,23 +600,31 @@ def run_b200(args):
     nbytes = dict(suite_bytes(ROWS, COLS))
     step_bytes = sum(nbytes.values())
 
+    # ---- sharded rows: sum_t(axis=0) is completed across the shards by the handler itself
+    # (H.set_comm: stream-ordered, no host wait), over the library's peer-memory kernel
+    peer_ok, comm = None, None
     if world > 1:
-        s0_torch = torch.as_tensor(t['s0'], device='cuda')
-
-    def finish_axis0():
-        """Cross-shard completion of the axis-0 sum: all-reduce of (1, COLS)."""
-        if world > 1:
-            check(lib.b200_sync())
-            dist.all_reduce(s0_torch)
-            torch.cuda.current_stream().synchronize()
+        from brainstorm_b200.parallel import Comm
+        comm = Comm()
+        peer_on = comm.enable_peer()
+        # self-check outside the timed region: the peer kernel against NCCL, replicas bit-equal
+        rs = np.random.RandomState(100 + rank)
+        x = rs.randn(COLS).astype(np.float32)
+        a_peer, a_nccl = H.create_from_numpy(x), H.create_from_numpy(x)
+        comm.allreduce(a_peer, 'sum')
+        check(lib.b200_comm_allreduce(a_nccl.ptr, a_nccl.size, 0)) if comm._lib_nccl else Comm(library_nccl=False).allreduce(a_nccl, 'sum')
+        got, want = H.get_numpy_copy(a_peer), H.get_numpy_copy(a_nccl)
+        gathered = [None] * world
+        dist.all_gather_object(gathered, got)
+        peer_ok = bool(peer_on and all(np.array_equal(g, gathered[0]) for g in gathered) and
+                       np.allclose(got, want, rtol=1e-6, atol=1e-6))
+        H.set_comm(comm, 'sum')
 
     def step(events=None):
         for i, (name, fn) in enumerate(suite):
             if events is not None:
                 check(lib.b200_event_record(events[i][0]))
             fn()
-            if name == 'sum_t_axis0':
-                finish_axis0()
             if events is not None:
                 check(lib.b200_event_record(events[i][1]))
 
@@ -591,38 +646,31 @@ def run_b200(args):
     barrier()
     t1 = time.time()
     launches = lib.b200_launch_count() - launches0
-    total_ms = elapsed(e_start, e_stop)
+    total_ms = _max_over_ranks(elapsed(e_start, e_stop), world)
     clocks = sampler.stop(t0, t1) if sampler else None
-    if world > 1:
-        tt = torch.tensor([total_ms], device='cuda')
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        total_ms = float(tt.item())
     ms_per_step = total_ms / args.steps
     value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
 
     op_ms = {}
     for i, (name, _) in enumerate(suite):
         op_ms[name] = float(np.mean([elapsed(*per_step_events[k][i]) for k in range(args.steps)]))
-    ops = {name: {'ms': round(ms, 4), 'gbs': round(nbytes[name] / (ms * 1e-3) / 1e9, 1)}
-           for name, ms in op_ms.items()}
+    ops = {name: [round(ms, 4), round(nbytes[name] / (ms * 1e-3) / 1e9)] for name, ms in op_ms.items()}
 
     if args.only == 'suite':
-        if rank == 0:
-            print(json.dumps({'metric': METRIC, 'value': round(value, 1), 'unit': UNIT, 'n_gpus': world,
-                              'steps': args.steps, 'ms_per_step': round(ms_per_step, 4),
-                              'config': {'workload': 'handler op suite only, (%d, %d)' % (ROWS, COLS)},
-                              'gpu_launches': int(launches), 'ops': ops}))
-        return
+        return finish({'metric': METRIC, 'value': round(value, 1), 'unit': UNIT, 'n_gpus': world,
+                       'steps': args.steps, 'ms_per_step': round(ms_per_step, 4),
+                       'config': {'workload': 'handler op suite only, (%d, %d)' % (ROWS, COLS)},
+                       'gpu_launches': int(launches), 'peer_ok': peer_ok, 'ops_ms_gbs': ops})
     # ---- end to end: host buffers in, results out, every step
     e2e_steps = max(2, min(args.steps, 4))
     results = [np.empty((1, COLS), np.float32), np.empty((ROWS, 1), np.float32),
                np.empty((), np.float32), np.empty((ROWS, 1), np.float32)]
-    h2d = sum(host[k].nbytes for k in ('a', 'b', 'dy', 'div', 'row', 'col', 'labels'))
+    names = ('a', 'b', 'dy', 'div', 'row', 'col', 'labels')
+    h2d = sum(host[k].nbytes for k in names)
     d2h = sum(r.nbytes for r in results)
 
     # Double-buffered operands: while the suite runs on one set, the next step's host
     # buffers are uploaded into the other set on the upload stream.
-    names = ('a', 'b', 'dy', 'div', 'row', 'col', 'labels')
     sets = [t, dict(t)]
     for k in names:
         sets[1][k] = H.allocate(t[k].shape)
@@ -642,8 +690,6 @@ def run_b200(args):
                 upload(nxt, done[nxt])                 # after the kernels that last read that set
             for name, fn in suites[cur]:
                 fn()
-                if name == 'sum_t_axis0':
-                    finish_axis0()
             done[cur] = H.record_event(done[cur] or None)
             for r, key in zip(results, ('s0', 's1', 'sall', 'picked')):
                 r[...] = H.get_numpy_copy(sets[cur][key])
@@ -654,27 +700,21 @@ def run_b200(args):
     w0 = time.perf_counter()
     e2e_run(e2e_steps)
     barrier()
-    e2e_s = (time.perf_counter() - w0) / e2e_steps
-    if world > 1:
-        tt = torch.tensor([e2e_s], device='cuda')
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        e2e_s = float(tt.item())
+    e2e_s = _max_over_ranks((time.perf_counter() - w0) / e2e_steps, world)
     e2e_value = world * step_bytes / e2e_s / 1e9
+    H.set_comm(None, 'local')
+    del t, suite, suites, sets, host
+    import gc
+    gc.collect()
 
-    lstm = lstm_training(H, world, rank, max(3, min(args.steps, 10)), barrier, lib, check)
-    del t, suite
-    others = other_training_configs(H, rank, lib) if world == 1 else \
-        {'mlp': sharded_training('mlp', H, world, rank, barrier, lib),
-         'highway_bn': sharded_training('highway_bn', H, world, rank, barrier, lib)}
+    gemm = gemm_block(H, lib, check, new_event, elapsed, local_rank, peaks)
+    lstm = lstm_training(H, world, rank, max(3, min(args.steps, 10)), barrier, lib)
+    others = {n: other_training(n, H, world, rank, barrier, lib, new_event, elapsed) for n in ('mlp', 'highway_bn')}
+    if comm is not None:
+        comm.close()
 
+    line = None
     if rank == 0:
-        peaks, peak_src = None, 'fallback'
-        try:
-            with open(os.path.join(ROOT, 'MEASURED_PEAKS.json')) as f:
-                peaks = json.load(f)
-            peak, peak_src = float(peaks['hbm_gbs']), 'measured'
-        except Exception:
-            peak = 6650.0
         traffic = None
         try:
             with open(os.path.join(ROOT, 'profiles', 'ncu_traffic.txt')) as f:
@@ -692,12 +732,13 @@ def run_b200(args):
             'metric': METRIC, 'value': round(value, 1), 'unit': UNIT, 'n_gpus': world,
             'steps': args.steps, 'warmup': max(args.warmup, 3), 'ms_per_step': round(ms_per_step, 4),
             'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32',
-            'data': 'synthetic (seeded block tiled down the rows)',
+            'data': 'synthetic (seeded draw of the whole operands)',
             'config': {'workload': 'handler op suite (27 ops), fp32 (%d, %d) operands per GPU, '
                                    '%.3g GiB each' % (ROWS, COLS, ROWS * COLS * 4 / 2.0 ** 30),
                        'rows_per_gpu': ROWS, 'cols': COLS, 'seed': SEED,
                        'l2': 'operands (1 GiB) exceed L2 (126 MB); no flush needed',
-                       'sharding': 'rows; axis-0 sum all-reduced over NCCL' if world > 1 else 'single GPU'},
+                       'sharding': 'rows; axis-0 sum completed across shards inside sum_t (peer-memory kernel)'
+                       if world > 1 else 'single GPU'},
             'e2e': {'value': round(e2e_value, 1), 'unit': UNIT, 'h2d_bytes_per_step': int(h2d),
                     'd2h_bytes_per_step': int(d2h), 'steps': e2e_steps},
             'gpu_launches': int(launches),
@@ -706,13 +747,14 @@ def run_b200(args):
                          'peak': peak, 'peak_source': peak_src, 'unit': 'GB/s',
                          'frac': round(achieved / peak, 4), 'traffic': traffic},
             'cpu_baseline': cpu,
-            'lstm': lstm,
+            'ops_ms_gbs': ops,
+            # the short blocks come last: the second half of the metric must survive a truncated record
+            'gemm': gemm,
             'other_training': others,
-            'ops': ops,
+            'peer_ok': peer_ok,
+            'lstm': lstm,
         }
-        print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+    finish(line)
 
 
 def run_gemm(args, H, lib, check, new_event, elapsed):
@@ -748,8 +790,9 @@ def main():
     ap.add_argument('--steps', type=int, default=30)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
-    ap.add_argument('--only', default='all', choices=['all', 'suite', 'gemm', 'lstm', 'mlp', 'highway_bn'],
-                    help='suite: device-resident op suite only; gemm: one dot_mm shape (for profiling)')
+    ap.add_argument('--only', default='all', choices=['all', 'suite', 'gemm', 'gemms', 'lstm', 'mlp', 'highway_bn'],
+                    help='suite: device-resident op suite only; gemm: one dot_mm shape (for profiling); '
+                         'gemms: the GEMM block of the bench line')
     ap.add_argument('--rows', type=int, default=ROWS, help='rows of the op-suite operands (default 65536)')
     ap.add_argument('--gemm', default='8192,4096,4096', help='M,N,K for --only gemm')
     args = ap.parse_args()

@@ -67,6 +67,7 @@ struct State {
   int gemm_bn = 0;    // 0 = auto, else forced tile width (32/64/128/256)
   int use_pdl = 1;    // programmatic dependent launch inside the LSTM time loops
   int gemm_pair = 0;   // 256-wide GEMM tiles on pairs of SMs (tcgen05 cta_group::2)
+  int gemm_chunk_kb = 0;     // k-blocks accumulated in tensor memory before a drain (0 = default)
   int sm_share = 1;   // split-K plans for sm_count / sm_share SMs (two streams sharing the GPU)
   bool pdl_now = false;  // set while a time loop is issuing its kernels
   // graph recording (b200_graph_begin .. b200_graph_end)

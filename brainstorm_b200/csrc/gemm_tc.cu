@@ -180,6 +180,10 @@ __device__ __forceinline__ float tf32_residual(float x) {
 // NV float4 of this thread (thread t owns float4 t, t + 128, ...).  All loads of a batch
 // of eight are issued before the first store, so their latencies overlap (the compiler
 // cannot reorder them itself: the two buffers may alias for all it knows).
+// Measured and not kept: rounding the residual to the nearest TF32 value before the store
+// (the tensor core truncates it otherwise) moves the bias of a product by 2e-7 and costs 8 %
+// of the kernel's throughput; rounding the landed tile itself to the nearest TF32 value and
+// writing it back (residuals of either sign) halves the bias and costs 30 %.
 template <int NV>
 __device__ __forceinline__ void split_tile(const float4* __restrict__ hi, float4* __restrict__ lo, int t) {
   constexpr int BATCH = NV < 8 ? NV : 8;
@@ -251,7 +255,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                    float* __restrict__ c, int M, int N, int K, int64_t ldc, int accumulate,
                    int a_mn_major, int b_mn_major, int* error_flag, int kb_per_split,
-                   int64_t split_stride) {
+                   int64_t split_stride, int chunk_kb) {
   using Cfg = TcConfig<BN>;
   constexpr int S = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -357,9 +361,9 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     for (int kb = 0; kb < num_kb && ok; ++kb) {
       const int s = kb % S;
       const uint32_t ph = (kb / S) & 1;
-      const int chunk = kb / TC_CHUNK_KB, buf = chunk & 1;
-      const bool chunk_first = (kb % TC_CHUNK_KB) == 0;
-      const bool chunk_last = (kb % TC_CHUNK_KB) == TC_CHUNK_KB - 1 || kb == num_kb - 1;
+      const int chunk = kb / chunk_kb, buf = chunk & 1;
+      const bool chunk_first = (kb % chunk_kb) == 0;
+      const bool chunk_last = (kb % chunk_kb) == chunk_kb - 1 || kb == num_kb - 1;
       if (chunk_first) {  // the buffer must have been drained (passes at once for chunks 0 and 1)
         ok = mbar_wait(acc_empty_bar(buf), ((chunk >> 1) & 1) ^ 1, abort_flag);
         if (!ok) break;
@@ -390,7 +394,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     const int t = threadIdx.x - 64;  // 0..127
     const int q = warp & 3;
     const uint32_t lane_bits = (uint32_t)(q * 32) << 16;
-    const int num_chunks = (num_kb + TC_CHUNK_KB - 1) / TC_CHUNK_KB;
+    const int num_chunks = (num_kb + chunk_kb - 1) / chunk_kb;
     constexpr bool kDrainsToo = Cfg::DRAIN_GROUPS == 2;
     float acc[kDrainsToo ? Cfg::ACC : 1];
 #pragma unroll
@@ -402,9 +406,9 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       const uint32_t ph = (kb / S) & 1;
       ok = mbar_wait(full_bar(s), ph, abort_flag);
       if (!ok) break;
-      const float4* ah = reinterpret_cast<const float4*>(smem + s * Cfg::STAGE_BYTES);
+      float4* ah = reinterpret_cast<float4*>(smem + s * Cfg::STAGE_BYTES);
       float4* al = reinterpret_cast<float4*>(smem + s * Cfg::STAGE_BYTES + Cfg::A_BYTES);
-      const float4* bh = reinterpret_cast<const float4*>(smem + s * Cfg::STAGE_BYTES + 2 * Cfg::A_BYTES);
+      float4* bh = reinterpret_cast<float4*>(smem + s * Cfg::STAGE_BYTES + 2 * Cfg::A_BYTES);
       float4* bl = reinterpret_cast<float4*>(smem + s * Cfg::STAGE_BYTES + 2 * Cfg::A_BYTES + Cfg::B_BYTES);
       split_tile<Cfg::A_BYTES / 16 / 128>(ah, al, t);
       split_tile<Cfg::B_BYTES / 16 / 128>(bh, bl, t);
@@ -450,7 +454,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     float acc[Cfg::ACC];
 #pragma unroll
     for (int j = 0; j < Cfg::ACC; ++j) acc[j] = 0.f;
-    const int num_chunks = (num_kb + TC_CHUNK_KB - 1) / TC_CHUNK_KB;
+    const int num_chunks = (num_kb + chunk_kb - 1) / chunk_kb;
     bool ok = true;
     for (int chunk = 0; chunk < num_chunks && ok; ++chunk) {
       const int buf = chunk & 1;
@@ -735,9 +739,9 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
       const uint32_t ph = (kb / S) & 1;
       ok = mbar_wait(full_bar(s), ph, abort_flag);
       if (!ok) break;
-      const float4* ah = reinterpret_cast<const float4*>(smem + s * Cfg::STAGE_BYTES);
+      float4* ah = reinterpret_cast<float4*>(smem + s * Cfg::STAGE_BYTES);
       float4* al = reinterpret_cast<float4*>(smem + s * Cfg::STAGE_BYTES + Cfg::A_BYTES);
-      const float4* bh = reinterpret_cast<const float4*>(smem + s * Cfg::STAGE_BYTES + 2 * Cfg::A_BYTES);
+      float4* bh = reinterpret_cast<float4*>(smem + s * Cfg::STAGE_BYTES + 2 * Cfg::A_BYTES);
       float4* bl = reinterpret_cast<float4*>(smem + s * Cfg::STAGE_BYTES + 2 * Cfg::A_BYTES + Cfg::B_BYTES);
       split_tile<Cfg::A_BYTES / 16 / 128>(ah, al, t);
       split_tile<Cfg::B_BYTES / 16 / 128>(bh, bl, t);
@@ -995,6 +999,15 @@ struct GemmPartials {
   int64_t ld;
 };
 
+// k-blocks accumulated in tensor memory between two drains (b200_set_tuning key 9).  Every
+// tcgen05.mma adds into its fp32 accumulator with truncation toward zero; with operands of
+// one sign the result of a chunk of c k-blocks comes out smaller by about c * 6.5e-7 of
+// itself (measured: 5.3e-6 / 2.6e-6 / 1.3e-6 / 7e-7 for c = 8 / 4 / 2 / 1, at 220 / 219 / 216 /
+// 209 TFLOP/s for 8192 x 4096 x 4096).  Two k-blocks (64 along K) is the default.
+static inline int chunk_k_blocks(const State& s) {
+  return (s.gemm_chunk_kb == 1 || s.gemm_chunk_kb == 2 || s.gemm_chunk_kb == 4 || s.gemm_chunk_kb == 8) ? s.gemm_chunk_kb : 2;
+}
+
 static int gemm_tc_impl(int transa, int transb, int64_t M, int64_t N, int64_t K, const float* a, int64_t lda,
                         const float* b, int64_t ldb, float* c, int64_t ldc, int accumulate,
                         GemmPartials* partials_out) {
@@ -1018,12 +1031,14 @@ static int gemm_tc_impl(int transa, int transb, int64_t M, int64_t N, int64_t K,
   // K range (a multiple of the TMEM chunk) and writes a partial tile; a second
   // kernel adds the partials in a fixed order.
   const int total_kb = (int)ceil_div(K, TC_BK);
+  const int chunk_kb = chunk_k_blocks(s);
   int splits = 1, kb_per_split = total_kb;
   const int64_t sms = s.sm_count / s.sm_share;
-  if (tiles * 2 <= sms && total_kb >= 2 * TC_CHUNK_KB) {
+  const int chunk_unit = chunk_kb > TC_CHUNK_KB ? chunk_kb : TC_CHUNK_KB;   // a split is a whole number of chunks (pair kernel: its own)
+  if (tiles * 2 <= sms && total_kb >= 2 * chunk_unit) {
     int want = (int)(sms / tiles);
     kb_per_split = (int)ceil_div(total_kb, want);
-    kb_per_split = (int)ceil_div(kb_per_split, TC_CHUNK_KB) * TC_CHUNK_KB;
+    kb_per_split = (int)ceil_div(kb_per_split, chunk_unit) * chunk_unit;
     splits = (int)ceil_div(total_kb, kb_per_split);
   }
   float* dst = c;
@@ -1085,10 +1100,10 @@ static int gemm_tc_impl(int transa, int transb, int64_t M, int64_t N, int64_t K,
                        (int)PairConfig::SMEM_BYTES, clusters);
     }
   } else switch (bn) {
-    case 32: B200_CUDA(launch_maybe_pdl(s.pdl_now, gemm_tf32x3_kernel<32>, grid, dim3(TC_THREADS), (size_t)TcConfig<32>::SMEM_BYTES, s.stream, ma, mb, dst, m, n, k, dst_ld, acc_flag, amn, bmn, flag, kb_per_split, split_stride)); break;
-    case 64: B200_CUDA(launch_maybe_pdl(s.pdl_now, gemm_tf32x3_kernel<64>, grid, dim3(TC_THREADS), (size_t)TcConfig<64>::SMEM_BYTES, s.stream, ma, mb, dst, m, n, k, dst_ld, acc_flag, amn, bmn, flag, kb_per_split, split_stride)); break;
-    case 256: B200_CUDA(launch_maybe_pdl(s.pdl_now, gemm_tf32x3_kernel<256>, grid, dim3(TC_THREADS), (size_t)TcConfig<256>::SMEM_BYTES, s.stream, ma, mb, dst, m, n, k, dst_ld, acc_flag, amn, bmn, flag, kb_per_split, split_stride)); break;
-    default: B200_CUDA(launch_maybe_pdl(s.pdl_now, gemm_tf32x3_kernel<128>, grid, dim3(TC_THREADS), (size_t)TcConfig<128>::SMEM_BYTES, s.stream, ma, mb, dst, m, n, k, dst_ld, acc_flag, amn, bmn, flag, kb_per_split, split_stride)); break;
+    case 32: B200_CUDA(launch_maybe_pdl(s.pdl_now, gemm_tf32x3_kernel<32>, grid, dim3(TC_THREADS), (size_t)TcConfig<32>::SMEM_BYTES, s.stream, ma, mb, dst, m, n, k, dst_ld, acc_flag, amn, bmn, flag, kb_per_split, split_stride, chunk_kb)); break;
+    case 64: B200_CUDA(launch_maybe_pdl(s.pdl_now, gemm_tf32x3_kernel<64>, grid, dim3(TC_THREADS), (size_t)TcConfig<64>::SMEM_BYTES, s.stream, ma, mb, dst, m, n, k, dst_ld, acc_flag, amn, bmn, flag, kb_per_split, split_stride, chunk_kb)); break;
+    case 256: B200_CUDA(launch_maybe_pdl(s.pdl_now, gemm_tf32x3_kernel<256>, grid, dim3(TC_THREADS), (size_t)TcConfig<256>::SMEM_BYTES, s.stream, ma, mb, dst, m, n, k, dst_ld, acc_flag, amn, bmn, flag, kb_per_split, split_stride, chunk_kb)); break;
+    default: B200_CUDA(launch_maybe_pdl(s.pdl_now, gemm_tf32x3_kernel<128>, grid, dim3(TC_THREADS), (size_t)TcConfig<128>::SMEM_BYTES, s.stream, ma, mb, dst, m, n, k, dst_ld, acc_flag, amn, bmn, flag, kb_per_split, split_stride, chunk_kb)); break;
   }
   B200_LAUNCH_CHECK();
   if (partials_out) {

@@ -7,6 +7,8 @@
 // rank (one process per GPU) owns a "window" of device memory that all other ranks of
 // the node have mapped (cudaIpc): two data slots and one arrival counter per rank.  One
 // CTA per call
+//   0. takes the next epoch from this rank's call counter (device memory, so a recorded
+//      call advances it on every replay),
 //   1. copies the local values into this rank's slot of the current epoch's parity,
 //   2. publishes the epoch to every rank's counter array (system-scope release store
 //      over NVLink),
@@ -36,13 +38,13 @@ constexpr int PEER_MAX_RANKS = 16;
 constexpr int PEER_MAX_FLOATS = 65536;                  // per call: 256 KiB per slot
 constexpr size_t PEER_SLOT_BYTES = (size_t)PEER_MAX_FLOATS * sizeof(float);
 constexpr size_t PEER_COUNTER_OFFSET = 2 * PEER_SLOT_BYTES;
-constexpr size_t PEER_WINDOW_BYTES = PEER_COUNTER_OFFSET + 256;   // counters: PEER_MAX_RANKS x 8 bytes, padded
+constexpr size_t PEER_CALLS_OFFSET = PEER_COUNTER_OFFSET + 128;  // this rank's own call counter (the epoch)
+constexpr size_t PEER_WINDOW_BYTES = PEER_COUNTER_OFFSET + 256;   // counters: PEER_MAX_RANKS x 8 bytes, the call counter, padding
 
 struct PeerState {
   int rank = -1, world = 0;
   bool disabled = false;                  // set when a wait ran out (see peer_disable)
   uint8_t* window[PEER_MAX_RANKS] = {};   // [rank] = own window, others = mapped peers
-  unsigned long long epoch = 0;           // host copy of the call counter
 } g_peer;
 
 struct PeerArgs {
@@ -61,8 +63,18 @@ __device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long
 
 __global__ void __launch_bounds__(1024)
 peer_allreduce_kernel(PeerArgs a, const float* src, float* dst, int n, int average,   // dst may be src
-                      unsigned long long epoch, int* error_flag, unsigned spin_limit) {
+                      int* error_flag, unsigned spin_limit) {
   __shared__ int timed_out;
+  __shared__ unsigned long long epoch_shared;
+  // The epoch is this rank's call counter.  It lives in the window, not in an argument, so
+  // that a call recorded into a graph takes the next epoch on every replay.
+  if (threadIdx.x == 0) {
+    unsigned long long* calls = reinterpret_cast<unsigned long long*>(a.window[a.rank] + PEER_CALLS_OFFSET);
+    epoch_shared = *calls + 1;
+    *calls = epoch_shared;
+  }
+  __syncthreads();
+  const unsigned long long epoch = epoch_shared;
   const int slot = (int)(epoch & 1);
   float* mine = reinterpret_cast<float*>(a.window[a.rank] + slot * PEER_SLOT_BYTES);
   if (threadIdx.x == 0) timed_out = 0;
@@ -173,7 +185,6 @@ B200_API int b200_peer_setup(int rank, int world, const uint64_t* windows) {
                        PEER_WINDOW_BYTES - PEER_COUNTER_OFFSET));
   g_peer.rank = rank;
   g_peer.world = world;
-  g_peer.epoch = 0;
   g_peer.disabled = false;
   for (int r = 0; r < world; ++r) g_peer.window[r] = (uint8_t*)(uintptr_t)windows[r];
   return B200_OK;
@@ -213,15 +224,13 @@ B200_API int b200_peer_allreduce(const float* src, float* dst, int n, int averag
   B200_REQUIRE(n >= 0 && n <= PEER_MAX_FLOATS, "at most %d floats per call", PEER_MAX_FLOATS);
   if (n == 0) return B200_OK;
   B200_REQUIRE(src != nullptr && dst != nullptr, "NULL operand");
-  B200_REQUIRE(!state().capturing, "a peer all-reduce cannot be recorded into a graph (its epoch is a call argument)");
   PeerArgs a;
   for (int r = 0; r < PEER_MAX_RANKS; ++r) a.window[r] = g_peer.window[r];
   a.rank = g_peer.rank;
   a.world = g_peer.world;
-  const unsigned long long epoch = ++g_peer.epoch;
   int threads = (n + 31) / 32 * 32;          // at least one warp (the ranks' counters are handled by threads 0..world-1)
   if (threads > 1024) threads = 1024;
-  peer_allreduce_kernel<<<1, threads, 0, state().stream>>>(a, src, dst, n, average, epoch, device_error_flag(),
+  peer_allreduce_kernel<<<1, threads, 0, state().stream>>>(a, src, dst, n, average, device_error_flag(),
                                                            state().peer_spin_limit);
   B200_LAUNCH_CHECK();
   return B200_OK;

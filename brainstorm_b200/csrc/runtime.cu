@@ -135,6 +135,8 @@ B200_API int b200_set_tuning(int key, int value) {
     case 5: s.use_pdl = value ? 1 : 0; break;
     case 7: s.gemm_pair = value ? 1 : 0; break;
     case 6: B200_REQUIRE(value >= 1 && value <= 8, "SM share divisor out of range"); s.sm_share = value; break;
+    case 9: B200_REQUIRE(value == 0 || value == 1 || value == 2 || value == 4 || value == 8, "chunk must be 0, 1, 2, 4 or 8 k-blocks");
+            s.gemm_chunk_kb = value; break;
     case 8: B200_REQUIRE(value >= 0 && value <= 30, "spin limit exponent out of range (0 = default)");
             s.peer_spin_limit = value ? (1u << value) : (1u << 22); break;
     default: return set_error(B200_ERR_ARG, "unknown tuning key %d", key);
@@ -378,6 +380,17 @@ B200_API int b200_memcpy_d2h(void* dst, uint64_t src, uint64_t bytes) {
   return gemm_tc_check_flag();
 }
 
+// Device -> page-locked host memory without waiting: the copy is queued on the library
+// stream behind the kernels that produce the data; the host reads `dst` after an event
+// recorded behind the copy has been reached (b200_event_record + b200_event_wait).
+B200_API int b200_memcpy_d2h_async(void* dst, uint64_t src, uint64_t bytes) {
+  if (int rc = require_ready()) return rc;
+  B200_NOT_WHILE_RECORDING("a device-to-host copy");
+  if (bytes)
+    B200_CUDA(cudaMemcpyAsync(dst, (const void*)(uintptr_t)src, (size_t)bytes, cudaMemcpyDeviceToHost, state().stream));
+  return B200_OK;
+}
+
 // Row-pitched transfers for strided views: `rows` rows of `row_bytes` bytes.
 B200_API int b200_memcpy2d_h2d(uint64_t dst, uint64_t dst_pitch, const void* src,
                                uint64_t src_pitch, uint64_t row_bytes, uint64_t rows) {
@@ -464,6 +477,12 @@ B200_API int b200_event_record(uint64_t ev) {
   B200_NOT_WHILE_RECORDING("recording an event");
   B200_CUDA(cudaEventRecord((cudaEvent_t)(uintptr_t)ev, state().stream));
   return B200_OK;
+}
+// Blocks the host until the event has been reached (nothing else is waited for).
+B200_API int b200_event_wait(uint64_t ev) {
+  B200_REQUIRE(ev != 0, "ev is NULL");
+  B200_CUDA(cudaEventSynchronize((cudaEvent_t)(uintptr_t)ev));
+  return gemm_tc_check_flag();
 }
 B200_API int b200_event_elapsed_ms(uint64_t start, uint64_t stop, float* ms) {
   B200_REQUIRE(ms != nullptr, "ms is NULL");

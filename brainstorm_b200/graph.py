@@ -162,8 +162,9 @@ class GraphedStepper(_StepperBase):
                 type(self.stepper).__name__, _scalars(self.stepper))
 
     def run(self):
-        if getattr(self.net.handler, '_comm', None) is not None:
-            return self.stepper.run()       # data parallel: the collectives are not recorded, run as usual
+        comm = getattr(self.net.handler, '_comm', None)
+        if comm is not None and not getattr(comm, 'capturable', False):
+            return self.stepper.run()       # data parallel over collectives that cannot be recorded: run as usual
         key = self._state_key()
         if key != self._key:
             self.invalidate()

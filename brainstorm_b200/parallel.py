@@ -26,9 +26,14 @@ import numpy as np
 
 
 class Comm(object):
-    """All-reduce over ``torch.distributed`` (initialised by the caller)."""
+    """All-reduce over the ranks of a ``torch.distributed`` group (initialised by the
+    caller; it is the rendezvous and carries host arrays).  Device arrays go through the
+    library's own entry points: ``b200_comm_allreduce`` (NCCL on the library's stream,
+    recordable into graphs) and, for small arrays after ``enable_peer``,
+    ``b200_peer_allreduce`` (one kernel over NVLink peer memory).  If the library cannot
+    find NCCL, device arrays fall back to the group's NCCL backend."""
 
-    def __init__(self):
+    def __init__(self, library_nccl=True):
         import torch.distributed as dist
         if not dist.is_initialized():
             raise RuntimeError('torch.distributed is not initialised')
@@ -36,8 +41,38 @@ class Comm(object):
         self.world = dist.get_world_size()
         self.rank = dist.get_rank()
         self._stream = None
+        self._lib_nccl = False    # device arrays go through b200_comm_allreduce
+        if library_nccl and self.world > 1:
+            self._join_library_communicator()
         self._peer_max = 0        # > 0: device arrays up to this many floats go over peer memory
         self._peer_windows = False   # this Comm registered peer windows that close() must release
+
+    def _join_library_communicator(self):
+        """Collective.  Rank 0 draws an NCCL id inside the library, the group hands it
+        round, every rank joins.  One communicator per process: a second ``Comm`` reuses it."""
+        import ctypes
+        import torch
+        from ._lib import lib
+        if not torch.cuda.is_available() or not lib.b200_stream():
+            return                                   # CPU ranks (gloo) or no handler yet
+        if lib.b200_comm_world() == self.world:
+            self._lib_nccl = True
+            return
+        ident = ctypes.create_string_buffer(128)
+        box = [ident.raw if (self.rank == 0 and lib.b200_comm_unique_id(ident) == 0) else None]
+        self.dist.broadcast_object_list(box, src=0)
+        ok = box[0] is not None and lib.b200_comm_init(self.rank, self.world, box[0]) == 0
+        agreed = [None] * self.world
+        self.dist.all_gather_object(agreed, ok)
+        if all(agreed):
+            self._lib_nccl = True
+        elif ok:
+            lib.b200_comm_destroy()
+
+    @property
+    def capturable(self):
+        """True if every device all-reduce of this object can be part of a recorded step."""
+        return self.world == 1 or self._lib_nccl
 
     def enable_peer(self):
         """Set up the library's all-reduce over NVLink peer memory for small device
@@ -147,6 +182,10 @@ class Comm(object):
         if self._peer_ok(arr):
             self._peer_allreduce(arr, op)     # a kernel on the library stream: nothing to wait for
             return None
+        if self._lib_nccl:
+            from ._lib import lib, check
+            check(lib.b200_comm_allreduce_async(arr.ptr, arr.size, 1 if op == 'avg' else 0))
+            return 'library'
         flat = arr.reshape((arr.size,))
         with torch.cuda.stream(self._device_stream()):
             t = torch.as_tensor(flat, device='cuda')
@@ -156,6 +195,10 @@ class Comm(object):
 
     def wait(self, handle):
         if handle is None:
+            return
+        if handle == 'library':             # the library stream waits for its communication stream
+            from ._lib import lib, check
+            check(lib.b200_comm_join())
             return
         work, host_avg = handle
         if host_avg is not None:
@@ -200,6 +243,10 @@ class Comm(object):
             return
         if self._peer_ok(arr):
             self._peer_allreduce(arr, op)
+            return
+        if self._lib_nccl:
+            from ._lib import lib, check
+            check(lib.b200_comm_allreduce(arr.ptr, arr.size, 1 if op == 'avg' else 0))
             return
         flat = arr.reshape((arr.size,))
         with torch.cuda.stream(self._device_stream()):
@@ -250,7 +297,7 @@ def _element_offset(view, flat):
 OVERLAP_MIN_BYTES = 32 << 20     # gradient vectors below this are all-reduced in one piece
 
 
-def data_parallel(net, comm, axis0_reduce='local', overlap=True, peer=False):
+def data_parallel(net, comm, axis0_reduce='local', overlap=True, peer=False, on_phase=None):
     """Make ``net`` (already on its handler) train data-parallel over ``comm``.
 
     Wraps ``net.backward_pass`` of this instance so that the flat gradient vector
@@ -267,7 +314,11 @@ def data_parallel(net, comm, axis0_reduce='local', overlap=True, peer=False):
 
     With ``peer`` (and a ``B200Handler``) all-reduces of small device arrays, i.e. the
     batch statistics, use the library's kernel over NVLink peer memory instead of a
-    library collective (``Comm.enable_peer``)."""
+    library collective (``Comm.enable_peer``).
+
+    ``on_phase`` (for measurements): called with ``'backward_queued'`` when the local
+    backward pass has been queued and with ``'reduced'`` when the work queued next will
+    see the averaged gradients."""
     handler = net.handler
     if not hasattr(handler, 'set_comm'):
         raise TypeError('handler %r cannot complete sums across ranks' % (handler,))
@@ -286,12 +337,16 @@ def data_parallel(net, comm, axis0_reduce='local', overlap=True, peer=False):
     def backward_pass():
         del pending[:]
         local_backward()
+        if on_phase is not None:
+            on_phase('backward_queued')
         if pending:
             for h in pending:
                 comm.wait(h)
             del pending[:]
         else:
             comm.allreduce(net.buffer.gradients, 'avg')
+        if on_phase is not None:
+            on_phase('reduced')
 
     net.backward_pass = backward_pass
 

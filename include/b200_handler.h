@@ -44,7 +44,10 @@ int b200_device_info(int* device, int* sm_count, uint64_t* free_bytes, uint64_t*
  * 7: 256-wide GEMM tiles on pairs of SMs (tcgen05 cta_group::2; default 0: measured slower
  *    than the single-SM tiles so far);
  * 8: the bounded wait of the peer all-reduce gives up after 2^value polls (0 = the default,
- *    2^22 polls, about 20 seconds). */
+ *    2^22 polls, about 20 seconds);
+ * 9: k-blocks of 32 that the tensor-core GEMM accumulates in tensor memory between two
+ *    drains into fp32 registers (1, 2, 4 or 8; 0 = the default, 2): shorter chunks lose
+ *    less to the tensor core's truncating accumulation and cost a little throughput. */
 int b200_set_tuning(int key, int value);
 uint64_t b200_stream(void);                            /* the main stream (a cudaStream_t) */
 /* A second compute stream, for work that may run beside the main stream's (a stack of
@@ -77,6 +80,10 @@ int b200_host_free(void* ptr);
  *      numpy_handler.py:60) ------------------------------------------------- */
 int b200_memcpy_h2d(uint64_t dst, const void* src, uint64_t bytes);
 int b200_memcpy_d2h(void* dst, uint64_t src, uint64_t bytes);             /* synchronises */
+/* The same without waiting, into page-locked memory: for the per-update read of the loss
+ * (Network.get_loss_values, brainstorm/structure/network.py:466), which a caller may take
+ * one step late; read dst after an event recorded behind the copy (b200_event_wait). */
+int b200_memcpy_d2h_async(void* dst, uint64_t src, uint64_t bytes);
 int b200_memcpy2d_h2d(uint64_t dst, uint64_t dst_pitch, const void* src, uint64_t src_pitch,
                       uint64_t row_bytes, uint64_t rows);
 int b200_memcpy2d_d2h(void* dst, uint64_t dst_pitch, uint64_t src, uint64_t src_pitch,
@@ -140,9 +147,32 @@ int b200_peer_enabled(void);
 int b200_peer_allreduce(const float* src, float* dst, int n, int average);
 int b200_peer_teardown(void);
 
+/* ---- all-reduce of device arrays over NCCL -----------------------------------
+ * The one exchange a batch-sharded run of the handler path needs: the flat gradient
+ * vector after Network.backward_pass, before the stepper reads it
+ * (brainstorm/training/steppers.py:61-69), and the sums over the batch axis that
+ * BatchNorm takes (brainstorm/layers/batch_normalization_layer.py:63-86,117-151).  One
+ * process per GPU.  Rank 0 asks for an id, the host hands its 128 bytes to every rank,
+ * every rank calls b200_comm_init (collective).  b200_comm_allreduce queues an in-place
+ * sum (average != 0: mean) on the library's current stream; b200_comm_allreduce_async
+ * queues it on a communication stream behind the work queued so far, so that kernels
+ * queued afterwards run beside it, until b200_comm_join.  All three can be recorded into
+ * a graph.  NCCL is looked up at run time (the copy already in the process, else
+ * libnccl.so.2, else the file named by B200_NCCL_LIB); without it b200_comm_init fails
+ * and the rest of the library is unaffected.  The reference has no counterpart (it has
+ * no multi-GPU code). */
+int b200_comm_unique_id(void* id /* 128 bytes */);
+int b200_comm_init(int rank, int world, const void* id /* 128 bytes */);
+int b200_comm_world(void);
+int b200_comm_allreduce(float* data, int64_t count, int average);
+int b200_comm_allreduce_async(float* data, int64_t count, int average);
+int b200_comm_join(void);
+int b200_comm_destroy(void);
+
 /* ---- CUDA-event timing on the library stream (benchmark support) --------- */
 int b200_event_create(uint64_t* ev);
 int b200_event_record(uint64_t ev);
+int b200_event_wait(uint64_t ev);                                         /* waits for this event only */
 int b200_event_elapsed_ms(uint64_t start, uint64_t stop, float* ms);      /* synchronises */
 int b200_event_destroy(uint64_t ev);
 

@@ -3,6 +3,7 @@
 import numpy as np
 import pytest
 
+import parity
 from conftest import needs_reference
 
 pytestmark = [pytest.mark.gpu, needs_reference]
@@ -32,15 +33,29 @@ def _close(got, want, rtol, what):
 
 
 def _close_l2(got, want, rtol, what):
-    """Norm-wise comparison for networks with kinks: a pre-activation that lies
-    within rounding distance of zero may fall on either side of a ReLU on the two
-    backends, which changes single entries by a whole delta but not the norm."""
     err = np.linalg.norm((got - want).ravel())
     ref = np.linalg.norm(want.ravel()) + 1e-30
     assert err <= rtol * ref, '%s: L2 err %.3g vs norm %.3g' % (what, err, ref)
 
 
-def _check_training(builder, steps, rtol, compare=None, fused=False, **kw):
+def _relu_flips(net_cpu, net_gpu):
+    """Units of the ReLU layers that are switched on on one backend and off on the other:
+    a pre-activation within rounding distance of zero may fall on either side."""
+    flips = 0
+    for lname, layer in net_cpu.layers.items():
+        if getattr(layer, 'activation', None) == 'rel':
+            path = lname + '.outputs.default'
+            flips += int(((net_cpu.get(path) > 0) != (net_gpu.get(path) > 0)).sum())
+    return flips
+
+
+# Observed on B200 (max error over max magnitude): gradients 1e-7 .. 1.7e-6, parameters after
+# the optimiser steps 4e-8 .. 2.1e-7, losses 0 .. 1.8e-7.  The bounds are ten times that.
+GRAD_TOL, PARAM_TOL, LOSS_TOL = 2e-5, 2e-6, 2e-6
+
+
+def _check_training(builder, steps, grad_tol=GRAD_TOL, param_tol=PARAM_TOL, compare=None, fused=False,
+                    after_first_pass=None, **kw):
     compare = compare or _close
     from brainstorm_b200.workloads import train_steps
     net_cpu, net_gpu, data, stepper = _pair(builder, fused=fused, **kw)
@@ -52,28 +67,70 @@ def _check_training(builder, steps, rtol, compare=None, fused=False, **kw):
     l_cpu = float(net_cpu.get_loss_values()['total_loss'])
     l_gpu = float(net_gpu.get_loss_values()['total_loss'])
     assert abs(l_cpu - l_gpu) <= 1e-5 * abs(l_cpu), (l_cpu, l_gpu)
-    compare(net_gpu.get('gradients'), net_cpu.get('gradients'), rtol, 'gradients')
+    compare(net_gpu.get('gradients'), net_cpu.get('gradients'), grad_tol, 'gradients')
+    if after_first_pass is not None:     # buffer-by-buffer checks while both sides still hold the same parameters
+        after_first_pass(net_cpu, net_gpu)
     # a few optimiser steps: losses and parameters stay together
     lc = train_steps(net_cpu, data, stepper(), steps)
     lg = train_steps(net_gpu, data, stepper(), steps)
-    np.testing.assert_allclose(lg, lc, rtol=2e-4)
-    compare(net_gpu.get('parameters'), net_cpu.get('parameters'), 10 * rtol, 'parameters')
+    np.testing.assert_allclose(lg, lc, rtol=LOSS_TOL)
+    compare(net_gpu.get('parameters'), net_cpu.get('parameters'), param_tol, 'parameters')
     return net_cpu, net_gpu
 
 
+def _lstm_buffers(T):
+    """Every internal, output, input delta and gradient of the LSTM layers, element by
+    element, against sums of |terms| (parity.lstm_net_checks)."""
+    def check(net_cpu, net_gpu):
+        worst = {}
+        parity.lstm_net_checks(net_cpu, net_gpu, T, worst)
+        parity.report(worst, 'LSTM buffers')
+    return check
+
+
 def test_mlp_dropout_fc_softmax_momentum():
+    """The ReLU network has kinks: where a pre-activation lies within rounding distance of
+    zero the two backends may disagree on which side, and the unit's whole delta then
+    appears in, or vanishes from, the gradient (observed: one unit of 240 000, moving the
+    gradient by 2.3e-3 of its norm).  So the flipped units are counted, and the gradient
+    bound allows for them and for nothing else; parameters and losses must agree closely
+    either way (the masks come from the same host generator on both sides)."""
     from brainstorm_b200 import workloads
-    _check_training(workloads.mlp, steps=3, rtol=2e-2, compare=_close_l2, batch=100)
+    seen = {}
+
+    def count(net_cpu, net_gpu):
+        seen['flips'] = _relu_flips(net_cpu, net_gpu)
+        assert seen['flips'] <= 4, seen
+
+    def gradients(got, want, tol, what):
+        if what == 'gradients':
+            flips = _relu_flips(*seen['nets'])
+            tol = tol + 3e-3 * flips
+        _close_l2(got, want, tol, what)
+
+    net_cpu, net_gpu, data, stepper = _pair(workloads.mlp, batch=100)
+    seen['nets'] = (net_cpu, net_gpu)
+    for net in (net_cpu, net_gpu):
+        net.provide_external_data(data)
+        net.forward_pass(training_pass=True)
+        net.backward_pass()
+    count(net_cpu, net_gpu)
+    gradients(net_gpu.get('gradients'), net_cpu.get('gradients'), GRAD_TOL, 'gradients')
+    from brainstorm_b200.workloads import train_steps
+    lc = train_steps(net_cpu, data, stepper(), 3)
+    lg = train_steps(net_gpu, data, stepper(), 3)
+    np.testing.assert_allclose(lg, lc, rtol=LOSS_TOL)
+    _close_l2(net_gpu.get('parameters'), net_cpu.get('parameters'), 1e-6, 'parameters')
 
 
 def test_lstm_two_layers_sgd():
     from brainstorm_b200 import workloads
-    _check_training(workloads.lstm, steps=2, rtol=2e-4, time=7, batch=9, vocab=23, hidden=32)
+    _check_training(workloads.lstm, steps=2, after_first_pass=_lstm_buffers(7), time=7, batch=9, vocab=23, hidden=32)
 
 
 def test_lstm_aligned_sizes_use_tensor_cores():
     from brainstorm_b200 import workloads
-    _check_training(workloads.lstm, steps=2, rtol=2e-4, time=6, batch=64, vocab=48, hidden=128)
+    _check_training(workloads.lstm, steps=2, after_first_pass=_lstm_buffers(6), time=6, batch=64, vocab=48, hidden=128)
 
 
 @pytest.mark.parametrize('shape', [dict(time=7, batch=9, vocab=23, hidden=32),
@@ -87,21 +144,7 @@ def test_fused_lstm_layer_matches_reference_layer(shape):
     NumpyHandler: loss, every gradient, parameters after SGD steps -- and every
     one of the twenty internal buffers plus outputs and input deltas."""
     from brainstorm_b200 import workloads
-    net_cpu, net_gpu = _check_training(workloads.lstm, steps=2, rtol=2e-4, fused=True, **shape)
-    for net in (net_cpu, net_gpu):
-        net.forward_pass(training_pass=True)
-        net.backward_pass()
-    for lname in net_cpu.layers:
-        if not lname.startswith('Lstm'):
-            continue
-        T = shape['time']
-        for kind in ('internals', 'outputs', 'input_deltas'):
-            for bname in net_cpu.buffer[lname][kind].keys():
-                path = '%s.%s.%s' % (lname, kind, bname)
-                c, g = net_cpu.get(path), net_gpu.get(path)
-                if c.shape[0] == T + 1:    # the context slot is not part of the pass
-                    c, g = c[:T], g[:T]
-                _close(g, c, 2e-4, path)
+    _check_training(workloads.lstm, steps=2, fused=True, after_first_pass=_lstm_buffers(shape['time']), **shape)
 
 
 @pytest.mark.parametrize('piece,shape', [(2, dict(time=7, batch=9, vocab=23, hidden=32)),
@@ -118,22 +161,8 @@ def test_stacked_fused_lstm_layers_side_by_side(piece, shape, monkeypatch):
     used = []
     real = lib.b200_use_stream
     monkeypatch.setattr(lib, 'b200_use_stream', lambda i: (used.append(i), real(i))[1])
-    net_cpu, net_gpu = _check_training(workloads.lstm, steps=2, rtol=2e-4, fused=True, **shape)
+    _check_training(workloads.lstm, steps=2, fused=True, after_first_pass=_lstm_buffers(shape['time']), **shape)
     assert used.count(1) >= 2 * 3            # forward and backward of (at least) three passes
-    for net in (net_cpu, net_gpu):
-        net.forward_pass(training_pass=True)
-        net.backward_pass()
-    T = shape['time']
-    for lname in net_cpu.layers:
-        if not lname.startswith('Lstm'):
-            continue
-        for kind in ('internals', 'outputs', 'input_deltas'):
-            for bname in net_cpu.buffer[lname][kind].keys():
-                path = '%s.%s.%s' % (lname, kind, bname)
-                c, g = net_cpu.get(path), net_gpu.get(path)
-                if c.shape[0] == T + 1:
-                    c, g = c[:T], g[:T]
-                _close(g, c, 2e-4, path)
 
 
 def test_fused_lstm_carries_context_between_calls():
@@ -148,12 +177,12 @@ def test_fused_lstm_carries_context_between_calls():
         ctx = net.get_context()
         net.forward_pass(training_pass=True, context=ctx)
         outs.append(net.get('Output_projection.outputs.default'))
-    _close(outs[1], outs[0], 1e-4, 'outputs of the second chunk')
+    _close(outs[1], outs[0], 2e-6, 'outputs of the second chunk')
 
 
 def test_highway_batchnorm_stack():
     from brainstorm_b200 import workloads
-    _check_training(workloads.highway_bn, steps=2, rtol=2e-4, batch=96, width=64, classes=10, blocks=3)
+    _check_training(workloads.highway_bn, steps=2, grad_tol=5e-6, batch=96, width=64, classes=10, blocks=3)
 
 
 def _two_sources(batch=6, time=3, n_in=12, n_out=5, seed=42, data_seed=0):
@@ -173,11 +202,11 @@ def _two_sources(batch=6, time=3, n_in=12, n_out=5, seed=42, data_seed=0):
 
 
 def test_hub_with_two_sources_hands_out_strided_views():
-    net_cpu, net_gpu = _check_training(_two_sources, steps=3, rtol=2e-5)
+    net_cpu, net_gpu = _check_training(_two_sources, steps=3, grad_tol=2e-6, param_tol=1e-6)
     assert not net_gpu.buffer['A'].outputs.default.is_contiguous
     assert not net_gpu.buffer['B'].output_deltas.default.is_contiguous
     for path in ('A.outputs.default', 'B.outputs.default', 'A.output_deltas.default', 'B.output_deltas.default'):
-        _close(net_gpu.get(path), net_cpu.get(path), 2e-5, path)
+        _close(net_gpu.get(path), net_cpu.get(path), 2e-6, path)
 
 
 def test_handler_is_describable_and_weight_modifier_runs():
@@ -235,9 +264,9 @@ def test_reference_trainer_with_iterators_and_hooks():
         logs.append((trainer.logs['rolling_training']['total_loss'], trainer.logs['valid_loss']['total_loss'],
                      net.get('parameters')))
         assert trainer.current_epoch_nr == 3 and trainer.current_update_nr == 12
-    np.testing.assert_allclose(logs[1][0], logs[0][0], rtol=2e-4)
-    np.testing.assert_allclose(logs[1][1], logs[0][1], rtol=2e-4)
-    _close_l2(logs[1][2], logs[0][2], 1e-3, 'parameters after 3 epochs')
+    np.testing.assert_allclose(logs[1][0], logs[0][0], rtol=2e-6)
+    np.testing.assert_allclose(logs[1][1], logs[0][1], rtol=2e-6)
+    _close_l2(logs[1][2], logs[0][2], 2e-6, 'parameters after 3 epochs')
 
 
 def test_device_one_hot_iterator_matches_host_one_hot():
@@ -261,5 +290,5 @@ def test_device_one_hot_iterator_matches_host_one_hot():
         it = onehot(bs.data_iterators.Minibatches(B, shuffle=False, default=idx, targets=tgt), {'default': V})
         trainer.train(net, it)
         results.append((trainer.logs['rolling_training']['total_loss'], net.get('parameters')))
-    np.testing.assert_allclose(results[1][0], results[0][0], rtol=1e-4)
-    _close(results[1][1], results[0][1], 2e-4, 'parameters')
+    np.testing.assert_allclose(results[1][0], results[0][0], rtol=2e-6)
+    _close(results[1][1], results[0][1], 2e-6, 'parameters')

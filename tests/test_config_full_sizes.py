@@ -212,23 +212,8 @@ def test_config2_labels_bit_exact(suite):
 # the scale of the sum times the factor), computed from the CPU run's own buffers.
 # Neither side is exact: NumpyHandler's float32 BLAS and the GPU's split-TF32 tensor-core
 # GEMM round differently, and what one rounding can move is proportional to that scale.
-RTOL = 1e-5
-
-
-def _A(x):
-    return np.abs(np.asarray(x, dtype=np.float32))
-
-
-def _bounded(got, want, scale, what, worst, rtol=RTOL):
-    got = np.asarray(got, np.float64)
-    want = np.asarray(want, np.float64)
-    assert got.shape == want.shape, (what, got.shape, want.shape)
-    err = np.abs(got - want)
-    bound = rtol * np.abs(want) + rtol * np.broadcast_to(np.asarray(scale, np.float64), want.shape) + 1e-37
-    ratio = float((err / bound).max()) if err.size else 0.0
-    worst[what] = ratio
-    assert ratio <= 1.0, '%s: %d of %d elements outside the bound, worst err/bound %.3g (err %.3g)' % (
-        what, int((err > bound).sum()), err.size, ratio, float(err.max()))
+RTOL = parity.REDUCTION_RTOL
+_A, _bounded, _report, _fc_checks = parity.absf, parity.bounded, parity.report, parity.fc_layer_checks
 
 
 def _pair(builder, fused=False, **kw):
@@ -252,21 +237,6 @@ def _pair(builder, fused=False, **kw):
     return net_cpu, net_gpu
 
 
-def _fc_checks(net_cpu, net_gpu, name, worst):
-    """A FullyConnected layer (fully_connected_layer.py:52-78): outputs against the sum of
-    |terms| of x.W^T + bias (the activations have slope <= 1), weight and bias gradients
-    against the sums of |terms| of their contractions over the batch."""
-    get = lambda net, path: net.get('%s.%s' % (name, path))
-    x = _A(get(net_cpu, 'inputs.default')).reshape(-1, get(net_cpu, 'inputs.default').shape[-1])
-    W, b = _A(get(net_cpu, 'parameters.W')), _A(get(net_cpu, 'parameters.bias'))
-    out = get(net_cpu, 'outputs.default')
-    _bounded(get(net_gpu, 'outputs.default'), out, (x @ W.T + b).reshape(out.shape), name + '.outputs', worst)
-    dH = _A(get(net_cpu, 'output_deltas.default')).reshape(-1, W.shape[0])   # overwritten with dout * f'(y) (:73)
-    _bounded(get(net_gpu, 'gradients.W'), get(net_cpu, 'gradients.W'), dH.T @ x, name + '.gradients.W', worst)
-    _bounded(get(net_gpu, 'gradients.bias'), get(net_cpu, 'gradients.bias'), dH.sum(0), name + '.gradients.bias', worst)
-    return dH @ W          # this layer's share of the sum of |terms| of its input deltas
-
-
 @needs_reference
 def test_config4_lstm_full_size_forward_backward():
     """Time 100, batch 128, 205 symbols, two LSTM layers of 1000 units (fused on the GPU),
@@ -276,69 +246,65 @@ def test_config4_lstm_full_size_forward_backward():
     T, B, H = 100, 128, 1000
     net_cpu, net_gpu = _pair(workloads.lstm, fused=True, time=T, batch=B, vocab=205, hidden=H, layers=2)
     worst = {}
-    for lname in [n for n in net_cpu.layers if n.startswith('Lstm')]:
-        cut = lambda v: v[:T] if v.ndim == 3 and v.shape[0] == T + 1 else v
-        get = lambda net, path: cut(net.get('%s.%s' % (lname, path)))
-        names = {kind: list(net_cpu.buffer[lname][kind].keys()) for kind in ('parameters', 'internals')}
-        S = parity.lstm_term_scales({k: get(net_cpu, 'parameters.' + k) for k in names['parameters']},
-                                    get(net_cpu, 'inputs.default'), get(net_cpu, 'outputs.default'),
-                                    {k: get(net_cpu, 'internals.' + k) for k in names['internals']},
-                                    get(net_cpu, 'output_deltas.default'))
-        for k in names['internals']:
-            _bounded(get(net_gpu, 'internals.' + k), get(net_cpu, 'internals.' + k), S[k], '%s.%s' % (lname, k), worst)
-        _bounded(get(net_gpu, 'outputs.default'), get(net_cpu, 'outputs.default'), S['y'], lname + '.outputs', worst)
-        _bounded(get(net_gpu, 'input_deltas.default'), get(net_cpu, 'input_deltas.default'), S['dx'],
-                 lname + '.input_deltas', worst)
-        for k in names['parameters']:
-            want = get(net_cpu, 'gradients.' + k)
-            _bounded(get(net_gpu, 'gradients.' + k), want, S['grad.' + k].reshape(want.shape),
-                     '%s.gradients.%s' % (lname, k), worst)
-    _fc_checks(net_cpu, net_gpu, 'Output_projection', worst)
-    k = max(worst, key=worst.get)
-    print('config 4 (T=100, B=128, 2 x 1000): worst err/bound %.3g at %s' % (worst[k], k))
+    parity.lstm_net_checks(net_cpu, net_gpu, T, worst)
+    _report(worst, 'config 4 (T=100, B=128, 2 x 1000)')
 
 
 @needs_reference
 def test_config5_highway_batchnorm_full_size_forward_backward():
     """Batch 8192, width 4096, ten Highway + BatchNorm blocks, 1000 classes: loss, every
-    layer's outputs and gradients, the batch statistics and the running statistics."""
+    layer's outputs and gradients, the batch statistics and the running statistics.
+
+    Scales follow the data flow: a buffer that combines the outputs of the two
+    FullyConnected layers carries their scales (the sums of |terms| of their 4096-term dot
+    products) times the factors they are multiplied with; the Highway carry path hands the
+    scale of the block's input on to its output, BatchNorm divides it by the batch standard
+    deviation; on the way back the deltas a block receives carry the scale the block above
+    attached to them."""
     from brainstorm_b200 import workloads
     net_cpu, net_gpu = _pair(workloads.highway_bn, batch=8192, width=4096, classes=1000, blocks=10)
     worst = {}
     m = 8192.0
+    g = lambda net, path: net.get(path)
+    shares, s_x = {}, 0.0
     for i in range(10):
-        share = sum(_fc_checks(net_cpu, net_gpu, n, worst) for n in ('H%d' % i, 'T%d' % i))
+        (s_h, share_h), (s_t, share_t) = (_fc_checks(net_cpu, net_gpu, n, worst) for n in ('H%d' % i, 'T%d' % i))
+        shares[i] = share_h + share_t
+        s_h, s_t = s_h[0], s_t[0]
         hw, bn = 'HW%d' % i, 'BN%d' % i
-        g = lambda net, path: net.get(path)
         x, Hh, Tt = (_A(g(net_cpu, '%s.inputs.%s' % (hw, k)))[0] for k in ('x', 'H', 'T'))
-        dy = _A(g(net_cpu, hw + '.output_deltas.default'))[0]
         # Highway (highway_layer.py:52-77): y = T*(H - x) + x
-        _bounded(g(net_gpu, hw + '.outputs.default'), g(net_cpu, hw + '.outputs.default'), Tt * (Hh + x) + x,
-                 hw + '.outputs', worst)
-        # deltas of the block's input: three sinks add into one buffer (H-FC, T-FC, Highway.x)
-        _bounded(g(net_gpu, hw + '.input_deltas.x'), g(net_cpu, hw + '.input_deltas.x'),
-                 share + (1 + Tt) * dy, hw + '.input_deltas.x', worst)
-        # BatchNorm forward (batch_normalization_layer.py:54-105)
-        xin = _A(g(net_cpu, bn + '.inputs.default'))[0]
+        s_hw = Tt * (Hh + x) + x + Tt * s_h + (Hh + x) * s_t + (1 + Tt) * s_x
+        _bounded(g(net_gpu, hw + '.outputs.default'), g(net_cpu, hw + '.outputs.default'), s_hw, hw + '.outputs', worst)
+        # BatchNorm forward (batch_normalization_layer.py:54-105); its input is the Highway output
         sig = g(net_cpu, bn + '.internals.sigma_b').astype(np.float64)
         gam, bet = (_A(g(net_cpu, '%s.parameters.%s' % (bn, k))) for k in ('gamma', 'beta'))
-        s_c = xin + xin.sum(0) / m                                 # centered = x - mean
-        _bounded(g(net_gpu, bn + '.internals.sigma_b'), sig, 0.0, bn + '.sigma_b', worst)
+        s_c = s_hw + s_hw.sum(0) / m                               # centered = x - mean
+        cen = _A(g(net_cpu, bn + '.internals.centered'))[0]
+        _bounded(g(net_gpu, bn + '.internals.sigma_b'), sig, (s_c * cen).sum(0) / m / sig, bn + '.sigma_b', worst)
         _bounded(g(net_gpu, bn + '.internals.centered'), g(net_cpu, bn + '.internals.centered'), s_c, bn + '.centered', worst)
         _bounded(g(net_gpu, bn + '.internals.x_hat'), g(net_cpu, bn + '.internals.x_hat'), s_c / sig, bn + '.x_hat', worst)
-        _bounded(g(net_gpu, bn + '.outputs.default'), g(net_cpu, bn + '.outputs.default'), s_c / sig * gam + bet,
-                 bn + '.outputs', worst)
+        s_x = (s_c / sig * gam + bet).astype(np.float32)           # the next block's input
+        _bounded(g(net_gpu, bn + '.outputs.default'), g(net_cpu, bn + '.outputs.default'), s_x, bn + '.outputs', worst)
         for k in ('mu', 'sigma'):                                  # running statistics, updated by the forward pass
             _bounded(g(net_gpu, '%s.parameters.%s' % (bn, k)), g(net_cpu, '%s.parameters.%s' % (bn, k)),
-                     xin.sum(0) / m, '%s.%s' % (bn, k), worst)
-        # BatchNorm backward (:107-152)
-        dout = _A(g(net_cpu, bn + '.output_deltas.default'))[0]
+                     s_hw.sum(0) / m, '%s.%s' % (bn, k), worst)
+    _, above = _fc_checks(net_cpu, net_gpu, 'Output_projection', worst)    # scale of the deltas it hands down
+    for i in range(9, -1, -1):
+        hw, bn = 'HW%d' % i, 'BN%d' % i
+        # BatchNorm backward (:107-152): dgamma, dbeta, and the three-term input delta
+        sig = g(net_cpu, bn + '.internals.sigma_b').astype(np.float64)
+        gam = _A(g(net_cpu, bn + '.parameters.gamma'))
+        dout = np.maximum(_A(g(net_cpu, bn + '.output_deltas.default'))[0], above)
         xh = _A(g(net_cpu, bn + '.internals.x_hat'))[0]
         s_dgamma, s_dbeta = (dout * xh).sum(0), dout.sum(0)
         _bounded(g(net_gpu, bn + '.gradients.gamma'), g(net_cpu, bn + '.gradients.gamma'), s_dgamma, bn + '.dgamma', worst)
         _bounded(g(net_gpu, bn + '.gradients.beta'), g(net_cpu, bn + '.gradients.beta'), s_dbeta, bn + '.dbeta', worst)
-        _bounded(g(net_gpu, bn + '.input_deltas.default'), g(net_cpu, bn + '.input_deltas.default'),
-                 (dout + xh * s_dgamma / m + s_dbeta / m) * gam / sig, bn + '.input_deltas', worst)
-    _fc_checks(net_cpu, net_gpu, 'Output_projection', worst)
-    k = max(worst, key=worst.get)
-    print('config 5 (8192 x 4096, 10 blocks): worst err/bound %.3g at %s' % (worst[k], k))
+        s_bn_in = (dout + xh * s_dgamma / m + s_dbeta / m) * gam / sig
+        _bounded(g(net_gpu, bn + '.input_deltas.default'), g(net_cpu, bn + '.input_deltas.default'), s_bn_in,
+                 bn + '.input_deltas', worst)
+        # deltas of the block's input: three sinks add into one buffer (H-FC, T-FC, Highway.x)
+        Tt = _A(g(net_cpu, hw + '.inputs.T'))[0]
+        above = (shares.pop(i) + (1 + Tt) * s_bn_in).astype(np.float32)
+        _bounded(g(net_gpu, hw + '.input_deltas.x'), g(net_cpu, hw + '.input_deltas.x'), above, hw + '.input_deltas.x', worst)
+    _report(worst, 'config 5 (8192 x 4096, 10 blocks)')
