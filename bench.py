@@ -514,11 +514,11 @@ def gemm_block(H, lib, check, new_event, elapsed, local_rank, peaks):
         clk = sampler.stop(t0, time.time())
         flop = 2.0 * M * N * K
         tf1, tfl = flop / min(single) / 1e9, flop / loop_ms / 1e9
-        out[name] = {'mnk': [M, N, K], 'single_tflops': round(tf1, 1), 'loop_tflops': round(tfl, 1),
-                     'frac_burst': round(tf1 / burst, 3), 'frac_sustained': round(tfl / sustained, 3),
-                     'loop_sm_mhz': clk.get('sm_mhz'), 'us': round(min(single) * 1e3, 1)}
+        out['%s_%dx%dx%d' % (name, M, N, K)] = [round(tf1, 1), round(tfl, 1), round(tf1 / burst, 3),
+                                                round(tfl / sustained, 3), clk.get('sm_mhz')]
         del a, b, c
-    out['peak_tflops'] = {'burst': round(burst, 1), 'sustained': round(sustained, 1)}
+    out['columns'] = 'single-call TFLOP/s, loop TFLOP/s, single/burst peak, loop/sustained peak, SM MHz in the loop'
+    out['peak_tflops'] = [round(burst, 1), round(sustained, 1)]
     return out
 
 

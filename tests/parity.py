@@ -168,10 +168,12 @@ def report(worst, title):
     assert not bad, '%s: outside the bound: %s' % (title, ', '.join('%s %.3g' % (k, worst[k]) for k in bad))
 
 
-def fc_layer_checks(net_cpu, net_gpu, name, worst, out_delta_scale=None):
+def fc_layer_checks(net_cpu, net_gpu, name, worst, out_delta_scale=None, in_scale=None):
     """A FullyConnected layer (brainstorm/layers/fully_connected_layer.py:52-78): outputs
     against the sum of |terms| of x.W^T + bias (the activations have slope <= 1), weight and
-    bias gradients against the sums of |terms| of their contractions over the batch.
+    bias gradients against the sums of |terms| of their contractions over the batch, in
+    which the deltas and the inputs enter with the scale their producer attached to them
+    (``out_delta_scale``, ``in_scale``) where that exceeds their magnitude.
     Returns (scale of the outputs, this layer's share of the scale of its input deltas)."""
     get = lambda net, path: net.get('%s.%s' % (name, path))
     xin = get(net_cpu, 'inputs.default')
@@ -183,7 +185,8 @@ def fc_layer_checks(net_cpu, net_gpu, name, worst, out_delta_scale=None):
     dH = absf(get(net_cpu, 'output_deltas.default')).reshape(-1, W.shape[0])   # overwritten with dout * f'(y) (:73)
     if out_delta_scale is not None:
         dH = np.maximum(dH, absf(out_delta_scale).reshape(dH.shape))
-    bounded(get(net_gpu, 'gradients.W'), get(net_cpu, 'gradients.W'), dH.T @ x, name + '.gradients.W', worst)
+    xg = x if in_scale is None else np.maximum(x, absf(in_scale).reshape(x.shape))
+    bounded(get(net_gpu, 'gradients.W'), get(net_cpu, 'gradients.W'), dH.T @ xg, name + '.gradients.W', worst)
     bounded(get(net_gpu, 'gradients.bias'), get(net_cpu, 'gradients.bias'), dH.sum(0), name + '.gradients.bias', worst)
     return s_out, dH @ W
 
@@ -193,7 +196,10 @@ def lstm_net_checks(net_cpu, net_gpu, T, worst):
     brainstorm.tools.create_net_from_spec), after one forward/backward pass on both sides:
     all twenty internals, outputs, input deltas and gradients of every LSTM layer, element
     by element, with the scales of lstm_term_scales."""
-    _, above = fc_layer_checks(net_cpu, net_gpu, 'Output_projection', worst)   # scale of the deltas it hands down
+    # scale of the deltas the output projection hands down: |dH| . |W|
+    dH = absf(net_cpu.get('Output_projection.output_deltas.default'))
+    above = dH.reshape(-1, dH.shape[-1]) @ absf(net_cpu.get('Output_projection.parameters.W'))
+    top_scale = None
     for lname in [n for n in net_cpu.layers if n.startswith('Lstm')][::-1]:
         cut = lambda v: v[:T] if v.ndim == 3 and v.shape[0] == T + 1 else v
         get = lambda net, path: cut(net.get('%s.%s' % (lname, path)))
@@ -204,6 +210,8 @@ def lstm_net_checks(net_cpu, net_gpu, T, worst):
                              {k: get(net_cpu, 'internals.' + k) for k in names['internals']},
                              get(net_cpu, 'output_deltas.default'), out_delta_scale=above.reshape(y.shape))
         above = S['dx']
+        if top_scale is None:
+            top_scale = S['y']
         for k in names['internals']:
             bounded(get(net_gpu, 'internals.' + k), get(net_cpu, 'internals.' + k), S[k], '%s.%s' % (lname, k), worst)
         bounded(get(net_gpu, 'outputs.default'), y, S['y'], lname + '.outputs', worst)
@@ -213,3 +221,4 @@ def lstm_net_checks(net_cpu, net_gpu, T, worst):
             want = get(net_cpu, 'gradients.' + k)
             bounded(get(net_gpu, 'gradients.' + k), want, S['grad.' + k].reshape(want.shape),
                     '%s.gradients.%s' % (lname, k), worst)
+    fc_layer_checks(net_cpu, net_gpu, 'Output_projection', worst, in_scale=top_scale)

@@ -289,7 +289,7 @@ def test_config5_highway_batchnorm_full_size_forward_backward():
         for k in ('mu', 'sigma'):                                  # running statistics, updated by the forward pass
             _bounded(g(net_gpu, '%s.parameters.%s' % (bn, k)), g(net_cpu, '%s.parameters.%s' % (bn, k)),
                      s_hw.sum(0) / m, '%s.%s' % (bn, k), worst)
-    _, above = _fc_checks(net_cpu, net_gpu, 'Output_projection', worst)    # scale of the deltas it hands down
+    _, above = _fc_checks(net_cpu, net_gpu, 'Output_projection', worst, in_scale=s_x)    # scale of the deltas it hands down
     for i in range(9, -1, -1):
         hw, bn = 'HW%d' % i, 'BN%d' % i
         # BatchNorm backward (:107-152): dgamma, dbeta, and the three-term input delta
