@@ -418,13 +418,17 @@ def other_training(name, H, world, rank, barrier, lib, new_event, elapsed):
         global_batch, steps, mode = 8192, 3 if world == 1 else 6, 'avg'
     net.set_handler(H)
     align_buffers(net)
-    phase_events = {}
+    phase_events, phases_on = {}, [False]
+
+    def mark(tag):
+        if phases_on[0]:
+            phase_events[tag] = H.record_event(phase_events.get(tag))
+
     if world > 1:
         from brainstorm_b200.parallel import Comm, data_parallel
         comm = Comm()
-        mark = (lambda tag: phase_events.__setitem__(tag, H.record_event(phase_events.get(tag)))) \
-            if name == 'highway_bn' else None
-        data_parallel(net, comm, axis0_reduce=mode, peer=(name == 'highway_bn'), on_phase=mark)
+        data_parallel(net, comm, axis0_reduce=mode, peer=(name == 'highway_bn'),
+                      on_phase=mark if name == 'highway_bn' else None)
     st = stepper()
     st.start(net)
 
@@ -437,8 +441,9 @@ def other_training(name, H, world, rank, barrier, lib, new_event, elapsed):
     ms, _ = _timed_steps(step, steps, barrier, world)
     out = {'samples_per_s': round(global_batch / ms * 1e3, 1), 'ms_per_step': round(ms, 3), 'global_batch': global_batch,
            'launches_per_step': int((lib.b200_launch_count() - l0) // (steps + 3))}
-    if phase_events:
+    if world > 1 and name == 'highway_bn':
         # one more step with the phases bracketed by events on the library stream
+        phases_on[0] = True
         fwd0 = net.forward_pass
 
         def forward_pass(*a, **k):
@@ -448,6 +453,7 @@ def other_training(name, H, world, rank, barrier, lib, new_event, elapsed):
         net.forward_pass = forward_pass
         step()
         mark('updated')
+        phases_on[0] = False
         net.forward_pass = fwd0
         H.synchronize()
         order = ['start', 'forward_done', 'backward_queued', 'reduced', 'updated']
