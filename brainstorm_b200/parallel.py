@@ -58,6 +58,12 @@ class Comm(object):
         if lib.b200_comm_world() == self.world:
             self._lib_nccl = True
             return
+        # The collectives run beside compute kernels that want (almost) every SM for themselves:
+        # a tensor-core GEMM CTA cannot share an SM with a collective's CTA (registers), so every
+        # SM the collective holds is one the next GEMM wave does not get.  Sixteen CTAs carry the
+        # gradient traffic of a step many times over; NCCL's default may take twice as many.
+        import os
+        os.environ.setdefault('NCCL_MAX_CTAS', '16')
         ident = ctypes.create_string_buffer(128)
         box = [ident.raw if (self.rank == 0 and lib.b200_comm_unique_id(ident) == 0) else None]
         self.dist.broadcast_object_list(box, src=0)
