@@ -578,6 +578,8 @@ def run_b200(args):
 
     if args.only == 'gemm':
         return run_gemm(args, H, lib, check, new_event, elapsed)
+    if args.only == 'ops':
+        return run_ops(args, H, lib, check, new_event, elapsed)
     if args.only == 'gemms':
         return finish({'metric': 'dot_mm_fp32_tflops', 'n_gpus': world,
                        'gemm': gemm_block(H, lib, check, new_event, elapsed, local_rank, peaks)})
@@ -763,6 +765,56 @@ def run_b200(args):
     finish(line)
 
 
+def run_ops(args, H, lib, check, new_event, elapsed):
+    """--only ops --ops a,b,...: the named ops of the suite, each `steps` times back to back,
+    on device-generated operands of (rows, 4096); only the operands those ops need are
+    allocated.  For profiler captures of single kernels and for launch-shape comparisons."""
+    rows = args.rows
+    want = [o for o in args.ops.split(',') if o]
+    t = {}
+    big = lambda: H.allocate((rows, COLS))
+    need = {'a'}
+    for o in want:
+        need |= {'out'} if not o.startswith(('sum_t', 'index')) else set()
+        need |= {'b'} if o in ('add_tt', 'subtract_tt', 'mult_tt') else set()
+        need |= {'div'} if o == 'divide_tt' else set()
+        need |= {'y', 'dy'} if o.endswith('_deriv') else set()
+        need |= {'absa'} if o == 'sqrt_t' else set()
+    for k in ('a', 'b', 'dy', 'div'):
+        if k in need:
+            t[k] = big()
+            H.fill_gaussian(0.5 if k == 'div' else 0.0, 2.0, t[k])
+    for k in ('out', 'y', 'absa'):
+        if k in need:
+            t[k] = big()
+    if 'y' in t:
+        H.tanh(t['a'], t['y'])
+    if 'absa' in t:
+        H.abs_t(t['a'], t['absa'])
+    t['row'], t['col'] = H.allocate((1, COLS)), H.allocate((rows, 1))
+    H.fill_gaussian(0.0, 1.0, t['row'])
+    H.fill_gaussian(0.0, 1.0, t['col'])
+    t['labels'] = H.create_from_numpy(np.random.RandomState(SEED).randint(0, COLS, (rows, 1)).astype(np.float32))
+    t['s0'], t['s1'], t['sall'], t['picked'] = H.zeros((1, COLS)), H.zeros((rows, 1)), H.zeros(()), H.zeros((rows, 1))
+    for k in ('a', 'b', 'dy', 'div', 'out', 'y', 'absa'):
+        t.setdefault(k, t['a'])
+    suite = dict(make_suite(H, t))
+    nbytes = dict(suite_bytes(rows, COLS))
+    res = {}
+    e0, e1 = new_event(), new_event()
+    for o in want:
+        for _ in range(max(args.warmup, 1)):
+            suite[o]()
+        check(lib.b200_event_record(e0))
+        for _ in range(args.steps):
+            suite[o]()
+        check(lib.b200_event_record(e1))
+        ms = elapsed(e0, e1) / args.steps
+        res[o] = [round(ms, 4), round(nbytes[o] / (ms * 1e-3) / 1e9)]
+    print(json.dumps({'metric': 'handler_op_throughput', 'unit': 'GB/s', 'config': {'workload': 'single ops, (%d, %d)' % (rows, COLS)},
+                      'steps': args.steps, 'ops_ms_gbs': res}))
+
+
 def run_gemm(args, H, lib, check, new_event, elapsed):
     """--only gemm: times dot_mm (a . b^T) at one shape on the tensor-core path and
     on the CUDA-core path; used for the ncu captures of the GEMM kernel."""
@@ -796,11 +848,12 @@ def main():
     ap.add_argument('--steps', type=int, default=30)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
-    ap.add_argument('--only', default='all', choices=['all', 'suite', 'gemm', 'gemms', 'lstm', 'mlp', 'highway_bn'],
+    ap.add_argument('--only', default='all', choices=['all', 'suite', 'ops', 'gemm', 'gemms', 'lstm', 'mlp', 'highway_bn'],
                     help='suite: device-resident op suite only; gemm: one dot_mm shape (for profiling); '
                          'gemms: the GEMM block of the bench line')
     ap.add_argument('--rows', type=int, default=ROWS, help='rows of the op-suite operands (default 65536)')
     ap.add_argument('--gemm', default='8192,4096,4096', help='M,N,K for --only gemm')
+    ap.add_argument('--ops', default='add_tt', help='comma-separated op names for --only ops')
     args = ap.parse_args()
     if args.impl == 'reference':
         run_reference(args)

@@ -16,9 +16,25 @@ struct Params {
 };
 
 // ---- functors -----------------------------------------------------------------
+// LAUNCH: 0 = 1024 threads x 32 blocks per SM (the default), 1 = 512 x 32, 2 = 1024 x 16.
+// Measured at 1 GiB per operand: the functors that spend many instructions per element
+// (expf, a correctly rounded square root or logarithm) gain 3-4 % from 512-thread blocks
+// (three resident blocks of ~40 registers instead of one of 1024 threads), tanh and the
+// sigmoid 1 % from the smaller grid; everything else is fastest at the default.
+#define B200_FUNCTOR_L(NAME, NIN_, LAUNCH_, EXPR)                              \
+  struct NAME {                                                                \
+    static constexpr int NIN = NIN_;                                           \
+    static constexpr int LAUNCH = LAUNCH_;                                     \
+    __device__ __forceinline__ static float apply(float a, float b, float c,   \
+                                                  const Params& p) {           \
+      (void)a; (void)b; (void)c; (void)p;                                      \
+      return EXPR;                                                             \
+    }                                                                          \
+  };
 #define B200_FUNCTOR(NAME, NIN_, EXPR)                                         \
   struct NAME {                                                                \
     static constexpr int NIN = NIN_;                                           \
+    static constexpr int LAUNCH = 0;                                           \
     __device__ __forceinline__ static float apply(float a, float b, float c,   \
                                                   const Params& p) {           \
       (void)a; (void)b; (void)c; (void)p;                                      \
@@ -61,13 +77,13 @@ B200_FUNCTOR(FFill, 0, p.p0)
 B200_FUNCTOR(FCopy, 1, a)
 B200_FUNCTOR(FAbs, 1, fabsf(a))
 B200_FUNCTOR(FSign, 1, sign_f(a))
-B200_FUNCTOR(FSqrt, 1, __fsqrt_rn(a))
-B200_FUNCTOR(FLog, 1, logf(a))
+B200_FUNCTOR_L(FSqrt, 1, 1, __fsqrt_rn(a))
+B200_FUNCTOR_L(FLog, 1, 1, logf(a))
 B200_FUNCTOR(FClip, 1, (a != a) ? a : fminf(fmaxf(a, p.p0), p.p1))
-B200_FUNCTOR(FSigmoid, 1, sigmoid_f(a))
-B200_FUNCTOR(FTanh, 1, tanhf(a))
+B200_FUNCTOR_L(FSigmoid, 1, 2, sigmoid_f(a))
+B200_FUNCTOR_L(FTanh, 1, 2, tanhf(a))
 B200_FUNCTOR(FRel, 1, (a > 0.0f) ? a : __fmul_rn(a, 0.0f))          // -0.0 / NaN like x*(x>0)
-B200_FUNCTOR(FEl, 1, el_f(a))
+B200_FUNCTOR_L(FEl, 1, 1, el_f(a))
 // derivative forms: a = y, b = dy
 B200_FUNCTOR(FSigmoidD, 2, __fmul_rn(__fmul_rn(b, a), __fsub_rn(1.0f, a)))
 B200_FUNCTOR(FTanhD, 2, __fmul_rn(b, __fsub_rn(1.0f, __fmul_rn(a, a))))
@@ -197,10 +213,10 @@ ew_pitched(const float* i0, const float* i1, const float* i2, float* out, int64_
   }
 }
 
-static inline int ew_grid(int64_t work_items, int threads) {
+static inline int ew_grid(int64_t work_items, int threads, int blocks_per_sm = 0) {
   const State& s = state();
   int64_t need = ceil_div(work_items, (int64_t)threads * EW_UNROLL);
-  int64_t cap = (int64_t)s.sm_count * s.ew_blocks_per_sm;
+  int64_t cap = (int64_t)s.sm_count * (blocks_per_sm ? blocks_per_sm : s.ew_blocks_per_sm);
   if (need < 1) need = 1;
   return (int)(need < cap ? need : cap);
 }
@@ -221,7 +237,10 @@ static int launch_ew(const float* i0, const float* i1, const float* i2, float* o
   const State& s = state();
   const bool contiguous = rows == 1 || ((F::NIN < 1 || ld0 == cols) && (F::NIN < 2 || ld1_ == cols) &&
                                         (F::NIN < 3 || ld2 == cols) && ldo == cols);
-  const int threads = s.ew_threads;
+  // the functor's own launch shape applies while the tuning knobs are at their defaults
+  const bool tuned = s.ew_threads != 1024 || s.ew_blocks_per_sm != 32;
+  const int threads = (!tuned && F::LAUNCH == 1) ? 512 : s.ew_threads;
+  const int bps = (!tuned && F::LAUNCH == 2) ? 16 : 0;
   if (!contiguous) {
     ew_pitched<F><<<ew_grid(n, threads), threads, 0, s.stream>>>(i0, i1, i2, out, rows, cols, ld0,
                                                                  ld1_, ld2, ldo, p);
@@ -240,7 +259,7 @@ static int launch_ew(const float* i0, const float* i1, const float* i2, float* o
     const float* q0 = i0 ? i0 + head : nullptr;
     const float* q1 = i1 ? i1 + head : nullptr;
     const float* q2 = i2 ? i2 + head : nullptr;
-    const int grid = ew_grid(nvec, threads);
+    const int grid = ew_grid(nvec, threads, bps);
     if (stream)
       ew_flat_vec<F, true><<<grid, threads, 0, s.stream>>>(q0, q1, q2, out + head, nvec, head, tail, p);
     else

@@ -27,3 +27,20 @@ def test_sharded_training_matches_global_batch():
     assert 'MULTI_GPU_OK' in out.stdout, out.stdout[-3000:] + out.stderr[-3000:]
     # the all-reduce over peer memory must really have been in use on this box
     assert 'PEER_ON' in out.stdout, out.stdout[-3000:]
+
+
+def test_all_reduce_through_the_c_abi_without_a_framework(tmp_path):
+    """b200_comm_*: a host that binds libb200handler.so and nothing else (no torch in the
+    worker processes) gets the gradient all-reduce, blocking, overlapped and recorded."""
+    import torch
+    gpus = torch.cuda.device_count()
+    if gpus < 2:
+        pytest.skip('needs two GPUs')
+    world = 2
+    env = dict(os.environ, NCCL_NVLS_ENABLE='0')
+    id_file = str(tmp_path / 'nccl_id')
+    procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, 'tests', 'comm_abi_worker.py'), str(r), str(world), id_file],
+                              stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=env) for r in range(world)]
+    outs = [p.communicate(timeout=300) for p in procs]
+    for p, (out, err) in zip(procs, outs):
+        assert p.returncode == 0 and 'COMM_ABI_OK' in out, out[-2000:] + err[-3000:]
