@@ -303,7 +303,7 @@ def _element_offset(view, flat):
 OVERLAP_MIN_BYTES = 32 << 20     # gradient vectors below this are all-reduced in one piece
 
 
-def data_parallel(net, comm, axis0_reduce='local', overlap=True, peer=False, on_phase=None):
+def data_parallel(net, comm, axis0_reduce='local', overlap=True, peer=True, on_phase=None):
     """Make ``net`` (already on its handler) train data-parallel over ``comm``.
 
     Wraps ``net.backward_pass`` of this instance so that the flat gradient vector
@@ -318,9 +318,10 @@ def data_parallel(net, comm, axis0_reduce='local', overlap=True, peer=False, on_
     Networks with gradient modifiers fall back to one all-reduce at the end, since
     the modifiers run inside the reference's backward_pass (network.py:445).
 
-    With ``peer`` (and a ``B200Handler``) all-reduces of small device arrays, i.e. the
-    batch statistics, use the library's kernel over NVLink peer memory instead of a
-    library collective (``Comm.enable_peer``).
+    With ``peer`` (the default, and a ``B200Handler``) all-reduces of small device arrays,
+    i.e. the batch statistics, use the library's kernel over NVLink peer memory instead of a
+    library collective (``Comm.enable_peer``; stays on NCCL if the ranks cannot map each
+    other's memory).
 
     ``on_phase`` (for measurements): called with ``'backward_queued'`` when the local
     backward pass has been queued and with ``'reduced'`` when the work queued next will
