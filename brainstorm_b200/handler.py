@@ -223,6 +223,12 @@ class B200Handler(Handler):
         check(lib.b200_device_info(_byref(dev), _byref(sms), _byref(free), _byref(total)))
         return dev.value, sms.value, free.value, total.value
 
+    def prepare_network(self, net):
+        """What a network should do to its buffers after ``net.set_handler(self)``: start
+        every hub on a 16-byte boundary (``brainstorm_b200.layout.align_buffers``)."""
+        from .layout import align_buffers
+        return align_buffers(net)
+
     def record(self, fn, *args, **kwargs):
         """Record the handler calls of ``fn(*args, **kwargs)`` instead of executing
         them; returns a ``RecordedStep`` whose ``launch()`` replays them with one
