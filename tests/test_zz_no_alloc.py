@@ -41,10 +41,10 @@ def test_static_scratch_sum_matches_scratch_sum_twice(rows, cols, axis):
 
 def test_static_scratch_rejects_oversize_and_does_not_touch_out():
     H, lib, check = _abi()
-    rows, cols = 256, 140000          # 2 row chunks x 140000 columns > 256 Ki floats
-    assert lib.b200_sum_t_scratch_floats(rows, cols, cols, 0) > lib.b200_sum_t_static_max_scratch_floats()
-    out = H.ones((cols,))
-    rc = lib.b200_sum_t_static(0, rows, cols, cols, 0, out.ptr)
+    rows, cols, ld = 300000, 3, 4         # the sum over everything of a pitched view keeps one partial per row
+    assert lib.b200_sum_t_scratch_floats(rows, cols, ld, -1) > lib.b200_sum_t_static_max_scratch_floats()
+    out = H.ones((1,))
+    rc = lib.b200_sum_t_static(0, rows, cols, ld, -1, out.ptr)
     assert rc != 0
     msg = lib.b200_last_error().decode()
     assert 'built-in array' in msg and 'b200_sum_t' in msg
