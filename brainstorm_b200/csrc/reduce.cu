@@ -269,30 +269,15 @@ nonfinite_kernel(const float* a, int64_t rows, int64_t cols, int64_t ld, int* fl
   if (__syncthreads_or(bad) && threadIdx.x == 0) atomicOr(flag, 1);
 }
 
-// Blocks of a pass-1 kernel that one SM holds at a time (registers decide: 80 per thread for
-// the 128-bit column sums).  The grids below are sized to ONE wave of resident blocks: with
-// more, the last wave is partly empty and the whole GPU waits for it (the column sums ran
-// 8 blocks per SM on 3 resident ones, 2.67 waves, and read at 6.2 instead of 6.8 TB/s).
-template <class K>
-static int resident_blocks(K kernel, int threads, int* cache) {
-  if (*cache > 0) return *cache;
-  if (!state().ready) return 2;       // asked before a GPU was bound: a guess, not remembered
-  int n = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, 0) != cudaSuccess || n < 1) {
-    cudaGetLastError();
-    n = 1;
-  }
-  *cache = n;
-  return n;
-}
-
+// Pass-1 grids are oversubscribed on purpose: `red_blocks_per_sm` (8) blocks per SM although
+// only three of the 128-bit column-sum blocks (80 registers) are resident at a time.  Short
+// blocks handed out dynamically even out what the memory system gives each SM; a grid of
+// exactly one resident wave was measured slower (column sums 6.20 -> 5.97 TB/s, sum over
+// everything 6.45 -> 6.31), because every SM then waits for the slowest block.
 static int axis0_plan(int64_t rows, int64_t cols, bool vec, int64_t* rows_per_chunk) {
   const State& s = state();
-  static int cache_vec = 0, cache_scalar = 0;
-  const int occ_vec = resident_blocks(sum_axis0_pass1<true>, 256, &cache_vec);
-  const int occ_scalar = resident_blocks(sum_axis0_pass1<false>, 256, &cache_scalar);
   const int64_t gx = ceil_div(cols, vec ? 128 : 32);
-  int64_t chunks = ((int64_t)s.sm_count * (vec ? occ_vec : occ_scalar)) / gx;   // rounded down: never a second wave
+  int64_t chunks = ceil_div((int64_t)s.sm_count * s.red_blocks_per_sm, gx);
   const int64_t max_chunks = ceil_div(rows, 64);  // at least 64 rows per chunk
   if (chunks > max_chunks) chunks = max_chunks;
   if (chunks > RED_MAX_PARTIALS) chunks = RED_MAX_PARTIALS;
@@ -303,10 +288,8 @@ static int axis0_plan(int64_t rows, int64_t cols, bool vec, int64_t* rows_per_ch
 
 static int all_plan(int64_t n, int64_t* chunk) {
   const State& s = state();
-  static int cache = 0;
-  const int occ = resident_blocks(sum_all_pass1<true>, RED_THREADS, &cache);
   int64_t blocks = ceil_div(n, (int64_t)RED_THREADS * 16);
-  const int64_t cap = (int64_t)s.sm_count * occ;
+  const int64_t cap = (int64_t)s.sm_count * s.red_blocks_per_sm;
   if (blocks > cap) blocks = cap;
   if (blocks > RED_MAX_PARTIALS) blocks = RED_MAX_PARTIALS;
   if (blocks < 1) blocks = 1;
