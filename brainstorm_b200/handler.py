@@ -83,14 +83,18 @@ class B200Handler(Handler):
             in-kernel Philox generator; ``'host'`` draws them from ``self.rnd``
             exactly like ``NumpyHandler`` (numpy_handler.py:193-200) and uploads
             them, for bit-parity runs.
+        align_hubs: start every hub of a network's flat buffer on a 16-byte boundary
+            (``brainstorm_b200.layout``): the reference packs hubs back to back, which
+            leaves most of them at odd element offsets, where kernels cannot use 128-bit
+            accesses and GEMM operands must be copied before TMA can fetch them.
     """
     __undescribed__ = {'context', 'dtype', 'EMPTY', 'rnd', 'device', 'seed', 'rng_mode',
                        '_scratch', '_flags', '_flag_host', '_rng_calls', '_label_check',
-                       '_pinned', '_comm', 'axis0_reduce'}
+                       '_pinned', '_comm', 'axis0_reduce', 'align_hubs'}
 
     array_type = B200Array
 
-    def __init__(self, seed=None, device=None, rng_mode='device'):
+    def __init__(self, seed=None, device=None, rng_mode='device', align_hubs=True):
         super(B200Handler, self).__init__()
         import os
         if device is None:
@@ -113,6 +117,7 @@ class B200Handler(Handler):
         self._pinned = []
         self._comm = None
         self.axis0_reduce = 'local'
+        self.align_hubs = bool(align_hubs)
 
     def __describe__(self):
         return {'@type': self.__class__.__name__}
@@ -122,6 +127,9 @@ class B200Handler(Handler):
 
     # ------------------------------------------------------------------ memory
     def allocate(self, shape):
+        if self.align_hubs and type(shape) is tuple and len(shape) == 1:
+            from .layout import align_calling_buffer_manager
+            align_calling_buffer_manager()
         return B200Array.empty(shape, zero=True)
 
     def zeros(self, shape):

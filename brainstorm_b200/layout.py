@@ -8,8 +8,11 @@ are (GEMM operands are copied into an aligned temporary first).
 
 ``align_buffers(net)`` makes the network's ``BufferManager`` start every hub on a multiple
 of four floats.  Only the slicing of the flat buffer changes: hub shapes, the layout, the
-views, parameter handling on a resize and everything else are the reference's own.  Call
-it after ``net.set_handler(B200Handler())``, like ``fuse_lstm_layers``.
+views, parameter handling on a resize and everything else are the reference's own.
+``B200Handler(align_hubs=True)`` (the default) arranges the same by itself the first time a
+``BufferManager`` asks it for its flat buffer, i.e. inside ``net.set_handler(handler)``; an
+explicit ``align_buffers(net)`` is only needed for a handler created with
+``align_hubs=False`` or to re-lay buffers that exist already.
 """
 from __future__ import annotations
 
@@ -27,11 +30,10 @@ def aligned_slices(shapes, floats=4):
     return pos, slices
 
 
-def align_buffers(net, floats=4):
-    """Re-lay the hubs of ``net`` on `floats`-element boundaries, now and on every later
-    resize.  Parameters are carried over.  Returns ``net``."""
+def install_aligned_resize(manager, floats=4):
+    """Give this ``BufferManager`` instance a ``resize`` that starts every hub on a multiple
+    of `floats` elements; takes effect at its next resize.  Returns the new method."""
     from brainstorm.structure.buffers import create_buffer_views_from_layout
-    manager = net._buffer_manager
 
     def resize(time_size, batch_size):
         # BufferManager.resize (buffers.py:69-96) with padded hub starts
@@ -55,9 +57,46 @@ def align_buffers(net, floats=4):
         return manager.views
 
     manager.resize = resize
+    manager._b200_aligned = True
+    return resize
+
+
+def align_buffers(net, floats=4):
+    """Re-lay the hubs of ``net`` on `floats`-element boundaries, now and on every later
+    resize.  Parameters are carried over.  Returns ``net``."""
+    manager = net._buffer_manager
+    resize = install_aligned_resize(manager, floats)
     # lay the current buffers out again (the padded total may exceed what is allocated)
     time_size, batch_size = manager.time_size, manager.batch_size
     manager.time_size = manager.batch_size = -1
     manager.size = -1
     net.buffer = resize(max(time_size, 0), max(batch_size, 0))
     return net
+
+
+def align_calling_buffer_manager(depth=2):
+    """Called by ``B200Handler.allocate``: if the caller `depth` frames up is
+    ``BufferManager.resize`` asking for its one flat buffer (structure/buffers.py:79), give
+    that manager the aligned ``resize`` for all later calls.  This is how a network gets
+    aligned hubs from ``net.set_handler(B200Handler())`` alone: ``set_handler`` makes the
+    manager resize to (0, 0) (buffers.py:98-108), which asks the new handler for memory."""
+    import sys
+    manager = None
+    for up in range(depth, depth + 3):      # a wrapping handler (DebugHandler) adds a frame or two
+        try:
+            frame = sys._getframe(up)
+        except ValueError:
+            return False
+        candidate = frame.f_locals.get('self')
+        if frame.f_code.co_name == 'resize' and type(candidate).__name__ == 'BufferManager':
+            manager = candidate
+            break
+    if manager is None:
+        return False
+    if getattr(manager, '_b200_aligned', False):
+        return True
+    try:
+        install_aligned_resize(manager)
+    except Exception:            # brainstorm is not importable or differs: leave the manager alone
+        return False
+    return True

@@ -55,7 +55,7 @@ def test_aligned_hubs_train_like_packed_hubs_on_the_gpu(which):
     results = []
     for align in (False, True):
         net, data, stepper = build()
-        net.set_handler(B200Handler(seed=7, rng_mode='host'))
+        net.set_handler(B200Handler(seed=7, rng_mode='host', align_hubs=False))
         if which == 'lstm':
             fuse_lstm_layers(net)
         if align:
@@ -68,3 +68,19 @@ def test_aligned_hubs_train_like_packed_hubs_on_the_gpu(which):
     for k in (1, 2):
         err = np.abs(results[1][k] - results[0][k]).max()
         assert err <= 2e-6 * np.abs(results[0][k]).max(), (k, err)
+
+
+@pytest.mark.gpu
+@needs_reference
+def test_set_handler_alone_gives_aligned_hubs():
+    """B200Handler(align_hubs=True), the default: the BufferManager gets the aligned resize
+    when it asks the handler for its flat buffer inside net.set_handler; nothing else to call."""
+    from brainstorm_b200 import B200Handler, workloads
+    for align in (True, False):
+        net, data, stepper = workloads.highway_bn(batch=24, width=12, classes=5, blocks=2)
+        net.set_handler(B200Handler(seed=7, align_hubs=align))
+        losses = workloads.train_steps(net, data, stepper(), 2)
+        assert np.isfinite(losses).all()
+        aligned = all(b.ptr % 16 == 0 for b in net._buffer_manager.buffers)
+        assert aligned == align
+        assert bool(getattr(net._buffer_manager, '_b200_aligned', False)) == align
