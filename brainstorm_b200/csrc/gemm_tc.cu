@@ -160,7 +160,13 @@ struct TcConfig {
   static constexpr int B_BYTES = BN * TC_BK * 4;
   static constexpr int STAGE_BYTES = 2 * (A_BYTES + B_BYTES);            // hi + lo of both
   static constexpr int STAGES = (BN >= 256) ? 2 : (BN >= 128) ? 3 : (BN >= 64) ? 4 : 5;
-  static constexpr int TMEM_COLS = 2 * BN;                               // two accumulator buffers
+  // Tiles of up to 128 columns keep the two small terms of the split (lo.hi, hi.lo) in an
+  // accumulator of their own: the tensor core truncates its accumulator at every MMA, and an
+  // addition of a small term to the large running sum loses as much as an addition of a
+  // large one.  Apart, only the hi.hi MMAs (a third of them) round at the large magnitude.
+  // 256-wide tiles have no tensor-memory columns left for it.
+  static constexpr bool SPLIT_ACC = BN <= 128;
+  static constexpr int TMEM_COLS = (SPLIT_ACC ? 4 : 2) * BN;             // two buffers of one or two accumulators
   // Register accumulators per thread are capped at 128: a 256-wide tile is drained by
   // two groups of four warps (the split-transform warps take columns [0, 128), the
   // drain warps [128, 256)); narrower tiles by the drain warps alone.
@@ -373,15 +379,17 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       tc_fence_after();
       if (lane == 0) {
         const uint32_t d = tmem_d + (uint32_t)(buf * BN);
+        const uint32_t d_small = Cfg::SPLIT_ACC ? tmem_d + (uint32_t)(2 * BN + buf * BN) : d;
 #pragma unroll
         for (int k = 0; k < TC_BK / 8; ++k) {
           const uint64_t dah = smem_desc(a_hi(s) + k * a_step, a_lbo, a_sbo, a_lt);
           const uint64_t dal = smem_desc(a_lo(s) + k * a_step, a_lbo, a_sbo, a_lt);
           const uint64_t dbh = smem_desc(b_hi(s) + k * b_step, b_lbo, b_sbo, b_lt);
           const uint64_t dbl = smem_desc(b_lo(s) + k * b_step, b_lbo, b_sbo, b_lt);
-          mma_tf32(d, dal, dbh, idesc, !(chunk_first && k == 0));   // small terms first
-          mma_tf32(d, dah, dbl, idesc, 1);
-          mma_tf32(d, dah, dbh, idesc, 1);
+          const uint32_t fresh = chunk_first && k == 0;             // first MMA of a chunk overwrites
+          mma_tf32(d_small, dal, dbh, idesc, !fresh);               // small terms first
+          mma_tf32(d_small, dah, dbl, idesc, 1);
+          mma_tf32(d, dah, dbh, idesc, Cfg::SPLIT_ACC ? !fresh : 1);
         }
         mma_commit(empty_bar(s));   // frees the stage once these MMAs have read it
         if (chunk_last) mma_commit(acc_full_bar(buf));
@@ -462,6 +470,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       __syncwarp();
       if (!ok) break;
       tc_fence_after();
+      if (Cfg::SPLIT_ACC) drain_add<Cfg::ACC>(tmem_d + lane_bits + (uint32_t)(2 * BN + buf * BN + COL0), acc);   // small terms first
       drain_add<Cfg::ACC>(tmem_d + lane_bits + (uint32_t)(buf * BN + COL0), acc);
       tc_fence_before();
       mbar_arrive(acc_empty_bar(buf));
@@ -1031,7 +1040,8 @@ static int gemm_tc_impl(int transa, int transb, int64_t M, int64_t N, int64_t K,
   // K range (a multiple of the TMEM chunk) and writes a partial tile; a second
   // kernel adds the partials in a fixed order.
   const int total_kb = (int)ceil_div(K, TC_BK);
-  const int chunk_kb = chunk_k_blocks(s);
+  // tiles of up to 128 columns keep the small terms in their own accumulator and can afford twice the chunk
+  const int chunk_kb = (bn <= 128 && s.gemm_chunk_kb == 0) ? 4 : chunk_k_blocks(s);
   int splits = 1, kb_per_split = total_kb;
   const int64_t sms = s.sm_count / s.sm_share;
   const int chunk_unit = chunk_kb > TC_CHUNK_KB ? chunk_kb : TC_CHUNK_KB;   // a split is a whole number of chunks (pair kernel: its own)

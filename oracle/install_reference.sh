@@ -15,8 +15,8 @@
 #
 # usage: oracle/install_reference.sh [reference checkout] [target dir]
 set -e
-REF=${1:-/root/reference}
 HERE=$(cd "$(dirname "$0")/.." && pwd)
+REF=${1:-${B200_REFERENCE_SRC:-$HERE/../reference}}
 DST=${2:-$HERE/baseline/_ref}
 TMP=$(mktemp -d /tmp/bsref.XXXXXX)
 
