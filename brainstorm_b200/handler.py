@@ -90,7 +90,7 @@ class B200Handler(Handler):
     """
     __undescribed__ = {'context', 'dtype', 'EMPTY', 'rnd', 'device', 'seed', 'rng_mode',
                        '_scratch', '_flags', '_flag_host', '_rng_calls', '_label_check',
-                       '_pinned', '_comm', 'axis0_reduce', 'align_hubs'}
+                       '_pinned', '_comm', 'axis0_reduce', 'align_hubs', '_axis0_skip'}
 
     array_type = B200Array
 
@@ -117,6 +117,7 @@ class B200Handler(Handler):
         self._pinned = []
         self._comm = None
         self.axis0_reduce = 'local'
+        self._axis0_skip = (0, 0)     # address range whose sums over the batch axis need no exchange of their own
         self.align_hubs = bool(align_hubs)
 
     def __describe__(self):
@@ -529,7 +530,9 @@ class B200Handler(Handler):
         sp, sn = self._scratch_for(need)
         check(lib.b200_sum_t(a.ptr, rows, cols, ld, ax, dst.ptr, sp, sn))
         if ax == 0 and self._comm is not None and self.axis0_reduce != 'local':
-            self._allreduce_axis0(dst)
+            lo, hi = self._axis0_skip
+            if not (lo <= out.ptr < hi):        # sums written into the gradient vector are averaged with it
+                self._allreduce_axis0(dst)
         if dst is not out:
             self.copy_to(dst.reshape(out.shape), out)
 
@@ -666,6 +669,7 @@ class B200Handler(Handler):
             raise ValueError("axis0_reduce must be 'local', 'sum' or 'avg'")
         self._comm = comm
         self.axis0_reduce = axis0_reduce
+        self._axis0_skip = (0, 0)
 
     def _allreduce_axis0(self, dst):
         self._comm.allreduce(dst, self.axis0_reduce)

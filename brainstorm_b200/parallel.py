@@ -343,6 +343,12 @@ def data_parallel(net, comm, axis0_reduce='local', overlap=True, peer=True, on_p
 
     def backward_pass():
         del pending[:]
+        if axis0_reduce == 'avg' and hasattr(handler, '_axis0_skip') and hasattr(net.buffer.gradients, 'ptr'):
+            # Sums over the batch axis that land in the gradient vector (bias gradients) are averaged
+            # with it below; completing each of them across the ranks first would be a second,
+            # redundant exchange.  (In 'avg' mode both give the same values.)
+            g = net.buffer.gradients
+            handler._axis0_skip = (g.ptr, g.ptr + 4 * g.size)
         local_backward()
         if on_phase is not None:
             on_phase('backward_queued')
