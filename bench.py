@@ -340,7 +340,6 @@ def lstm_training(H, world, rank, steps, barrier, lib):
         return {'unavailable': why}
     from brainstorm_b200 import workloads
     from brainstorm_b200.fused_lstm import fuse_lstm_layers
-    from brainstorm_b200.layout import align_buffers
     from brainstorm_b200.pipeline import PrefetchingIterator, defer_loss_readback
     T, B = 100, 128
     net, data, stepper = workloads.lstm(time=T, batch=B, data_seed=rank)
@@ -350,7 +349,6 @@ def lstm_training(H, world, rank, steps, barrier, lib):
         pinned[k][...] = v
     net.set_handler(H)
     fuse_lstm_layers(net)
-    align_buffers(net)
     st = stepper()
     st.start(net)
 
@@ -409,15 +407,18 @@ def other_training(name, H, world, rank, barrier, lib, new_event, elapsed):
     if why:
         return {'unavailable': why}
     from brainstorm_b200 import GraphedStepper, workloads
-    from brainstorm_b200.layout import align_buffers
     if name == 'mlp':
         net, data, stepper = workloads.mlp(batch=100, data_seed=rank)
         global_batch, steps, mode = 100 * world, 50, 'local'
     else:
         net, data, stepper = workloads.highway_bn(batch=8192 // world, data_seed=rank)
         global_batch, steps, mode = 8192, 3 if world == 1 else 6, 'avg'
+    pinned = {}
+    for k, v in data.items():                     # host batches live in page-locked memory, as in lstm_training
+        pinned[k] = H.pinned_empty(v.shape, np.float32)
+        pinned[k][...] = v
+    host_data, data = data, pinned
     net.set_handler(H)
-    align_buffers(net)
     phase_events, phases_on = {}, [False]
 
     def mark(tag):
@@ -481,7 +482,7 @@ def other_training(name, H, world, rank, barrier, lib, new_event, elapsed):
             from brainstorm_b200.pipeline import PrefetchingIterator, defer_loss_readback
             n = 200
             batch = data['default'].shape[1]
-            many = {k: np.concatenate([v] * n, axis=1) for k, v in data.items()}
+            many = {k: np.concatenate([v] * n, axis=1) for k, v in host_data.items()}
             it = PrefetchingIterator(bs.data_iterators.Minibatches(batch, shuffle=False, **many))
             deferred = defer_loss_readback(net)
             barrier()
