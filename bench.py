@@ -468,6 +468,15 @@ def other_training(name, H, world, rank, barrier, lib, new_event, elapsed):
         st.run()
         out['host_queue_ms'] = round(_max_over_ranks((time.perf_counter() - t0), world) * 1e3, 3)
         H.synchronize()
+    if name == 'highway_bn':
+        # the same network with the Highway, BatchNorm and FullyConnected layers in their fused forms (same bits);
+        # the recorded step below runs them too
+        from brainstorm_b200.fused_layers import fuse_layers
+        fuse_layers(net)
+        l0 = lib.b200_launch_count()
+        ms, _ = _timed_steps(step, steps, barrier, world)
+        out['fused_layers'] = {'ms_per_step': round(ms, 3), 'samples_per_s': round(global_batch / ms * 1e3, 1),
+                               'launches_per_step': int((lib.b200_launch_count() - l0) // (steps + 3))}
     if name == 'mlp' or world > 1:
         gs = GraphedStepper(stepper(), eager_steps=1)
         gs.start(net)

@@ -402,6 +402,57 @@ static int launch_mv(const float* m, const float* v, float* out, int64_t rows, i
   return B200_OK;
 }
 
+// out[r, c] = f(out[r, c] + bias[c]) in place: the tail of FullyConnectedLayerImpl.forward_pass
+// (brainstorm/layers/fully_connected_layer.py:61-62: add_mv, then the in-place activation) as one
+// kernel.  Same walk as mv_vec; the sum is rounded before the activation is applied, as there.
+template <class F>
+__global__ void __launch_bounds__(1024)
+bias_act_vec(float* out, const float* bias, int64_t rows, int cols4, int64_t ld, Params p) {
+  const int c4 = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c4 >= cols4) return;
+  const float4 b = *reinterpret_cast<const float4*>(bias + 4 * (int64_t)c4);
+  const int64_t rstride = (int64_t)gridDim.y * blockDim.y;
+  for (int64_t r0 = (int64_t)blockIdx.y * blockDim.y + threadIdx.y; r0 < rows; r0 += rstride * EW_UNROLL) {
+    float4 a[EW_UNROLL];
+#pragma unroll
+    for (int u = 0; u < EW_UNROLL; ++u) {
+      const int64_t r = r0 + u * rstride;
+      a[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (r < rows) a[u] = *reinterpret_cast<const float4*>(out + r * ld + 4 * (int64_t)c4);
+    }
+#pragma unroll
+    for (int u = 0; u < EW_UNROLL; ++u) {
+      const int64_t r = r0 + u * rstride;
+      if (r >= rows) continue;
+      float4 v;
+      v.x = F::apply(__fadd_rn(a[u].x, b.x), 0.f, 0.f, p);
+      v.y = F::apply(__fadd_rn(a[u].y, b.y), 0.f, 0.f, p);
+      v.z = F::apply(__fadd_rn(a[u].z, b.z), 0.f, 0.f, p);
+      v.w = F::apply(__fadd_rn(a[u].w, b.w), 0.f, 0.f, p);
+      *reinterpret_cast<float4*>(out + r * ld + 4 * (int64_t)c4) = v;
+    }
+  }
+}
+
+template <class F>
+static int launch_bias_act(float* out, const float* bias, int64_t rows, int64_t cols, int64_t ld) {
+  const State& s = state();
+  const int cols4 = (int)(cols / 4);
+  const int tx = cols4 >= 256 ? 256 : (cols4 >= 128 ? 128 : (cols4 >= 64 ? 64 : 32));
+  int ty = s.ew_threads / tx;
+  if (ty < 1) ty = 1;
+  while (ty > 1 && (int64_t)ty * EW_UNROLL > rows) ty >>= 1;
+  const int gx = (int)ceil_div(cols4, tx);
+  int64_t gy = ceil_div((int64_t)s.sm_count * s.ew_blocks_per_sm, gx);
+  const int64_t gy_max = ceil_div(rows, (int64_t)ty * EW_UNROLL);
+  if (gy > gy_max) gy = gy_max;
+  if (gy > 65535) gy = 65535;
+  if (gy < 1) gy = 1;
+  bias_act_vec<F><<<dim3(gx, (unsigned)gy), dim3(tx, ty), 0, s.stream>>>(out, bias, rows, cols4, ld, Params{0.f, 0.f});
+  B200_LAUNCH_CHECK();
+  return B200_OK;
+}
+
 // ---- labels ---------------------------------------------------------------------
 // out[r, c] = (c == int(v[r])) ? 1 : 0 ; every element of out is written once.
 // A thread owns one float4 column group (or one column) and walks down the rows
@@ -632,4 +683,20 @@ B200_API int b200_split_add_tt(const float* x, float* out_a, float* out_b, int64
   split_add_kernel<<<ew_grid(rows * (na + nb) * EW_UNROLL, 256), 256, 0, state().stream>>>(x, out_a, out_b, rows, na, nb);
   B200_LAUNCH_CHECK();
   return B200_OK;
+}
+
+// act: 0 sigmoid, 1 tanh, 2 rel, 3 el, 4 linear (bias only).  cols and ld multiples of 4, 16-byte aligned operands.
+B200_API int b200_bias_act(float* out, const float* bias, int64_t rows, int64_t cols, int64_t ld, int act) {
+  if (int rc = require_ready()) return rc;
+  B200_REQUIRE(rows >= 0 && cols >= 0 && act >= 0 && act <= 4, "bad extent or activation code");
+  if (rows * cols == 0) return B200_OK;
+  B200_REQUIRE(out && bias && cols % 4 == 0 && ld % 4 == 0 && ld >= cols && aligned16(out) && aligned16(bias) &&
+               cols < ((int64_t)1 << 31), "bias_act needs 16-byte aligned operands and a multiple of 4 columns");
+  switch (act) {
+    case 0: return launch_bias_act<FSigmoid>(out, bias, rows, cols, ld);
+    case 1: return launch_bias_act<FTanh>(out, bias, rows, cols, ld);
+    case 2: return launch_bias_act<FRel>(out, bias, rows, cols, ld);
+    case 3: return launch_bias_act<FEl>(out, bias, rows, cols, ld);
+    default: return launch_bias_act<FCopy>(out, bias, rows, cols, ld);
+  }
 }

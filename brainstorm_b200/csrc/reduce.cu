@@ -125,6 +125,87 @@ sum_axis0_pass1(const float* a, int64_t rows, int64_t cols, int64_t ld, int64_t 
   }
 }
 
+// ---- column sums with the producing elementwise step folded in (BatchNorm) -------------
+// The BatchNorm layer (brainstorm/layers/batch_normalization_layer.py) takes every one of its
+// batch statistics as "an elementwise op into a temporary, then sum_t(axis=0)".  These two
+// pass-1 kernels do the elementwise step while they read, with exactly the row walk and the
+// order of additions of sum_axis0_pass1<true>, so the sums have the same bits as the two-call
+// form; pass 2 is sum_axis0_pass2.  128-bit accesses: cols and ld multiples of 4, 16-byte
+// aligned bases.
+//   MODE 0 (forward, :67-86): c = x + mu[col] is written to `centered`; sums of c * c.
+//   MODE 1 (backward, :121-136): sums of dout * x_hat (to dst) and of dout (to dst2).
+template <int MODE>
+__global__ void __launch_bounds__(256)
+bn_colsum_pass1(const float* a, const float* b, const float* vec, float* centered, int64_t rows, int64_t cols,
+                int64_t rows_per_chunk, float* dst, float* dst2) {
+  __shared__ float smem[8][32 * 4 + 1];
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const int64_t c = ((int64_t)blockIdx.x * 32 + tx) * 4;
+  const int64_t r_lo = (int64_t)blockIdx.y * rows_per_chunk;
+  int64_t r_hi = r_lo + rows_per_chunk;
+  if (r_hi > rows) r_hi = rows;
+  constexpr int U = 8;
+  constexpr int SETS = MODE == 1 ? 2 : 1;
+  float acc[SETS][U][4];
+#pragma unroll
+  for (int s = 0; s < SETS; ++s)
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int w = 0; w < 4; ++w) acc[s][u][w] = 0.f;
+  if (c < cols) {
+    float4 mu = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (MODE == 0) mu = *reinterpret_cast<const float4*>(vec + c);
+    auto take = [&](int u, float4 va, float4 vb, int64_t r) {
+      if (MODE == 0) {
+        const float4 cv = make_float4(__fadd_rn(va.x, mu.x), __fadd_rn(va.y, mu.y), __fadd_rn(va.z, mu.z),
+                                      __fadd_rn(va.w, mu.w));
+        *reinterpret_cast<float4*>(centered + r * cols + c) = cv;
+        acc[0][u][0] += __fmul_rn(cv.x, cv.x); acc[0][u][1] += __fmul_rn(cv.y, cv.y);
+        acc[0][u][2] += __fmul_rn(cv.z, cv.z); acc[0][u][3] += __fmul_rn(cv.w, cv.w);
+      } else {
+        acc[0][u][0] += __fmul_rn(va.x, vb.x); acc[0][u][1] += __fmul_rn(va.y, vb.y);
+        acc[0][u][2] += __fmul_rn(va.z, vb.z); acc[0][u][3] += __fmul_rn(va.w, vb.w);
+        acc[SETS - 1][u][0] += va.x; acc[SETS - 1][u][1] += va.y; acc[SETS - 1][u][2] += va.z; acc[SETS - 1][u][3] += va.w;
+      }
+    };
+    int64_t r = r_lo + ty;
+    for (; r + 8 * (U - 1) < r_hi; r += 8 * U) {
+      float4 va[U], vb[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        va[u] = *reinterpret_cast<const float4*>(a + (r + 8 * u) * cols + c);
+        if (MODE == 1) vb[u] = *reinterpret_cast<const float4*>(b + (r + 8 * u) * cols + c);
+        else vb[u] = va[u];
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) take(u, va[u], vb[u], r + 8 * u);
+    }
+    for (; r < r_hi; r += 8) {
+      const float4 va = *reinterpret_cast<const float4*>(a + r * cols + c);
+      const float4 vb = MODE == 1 ? *reinterpret_cast<const float4*>(b + r * cols + c) : va;
+      take(0, va, vb, r);
+    }
+  }
+#pragma unroll
+  for (int s = 0; s < SETS; ++s) {
+#pragma unroll
+    for (int w = 0; w < 4; ++w)
+      smem[ty][tx * 4 + w] = ((acc[s][0][w] + acc[s][1][w]) + (acc[s][2][w] + acc[s][3][w])) +
+                             ((acc[s][4][w] + acc[s][5][w]) + (acc[s][6][w] + acc[s][7][w]));
+    __syncthreads();
+    float* out = s == 0 ? dst : dst2;
+    for (int j = ty * 32 + tx; j < 32 * 4; j += 256) {
+      float t = 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) t += smem[k][j];
+      const int64_t cc = (int64_t)blockIdx.x * 32 * 4 + j;
+      if (cc < cols) out[(int64_t)blockIdx.y * cols + cc] = t;
+    }
+    __syncthreads();
+  }
+}
+
 // out[c] = sum over chunks of partial[chunk * cols + c], fixed order
 __global__ void __launch_bounds__(256)
 sum_axis0_pass2(const float* partial, int chunks, int64_t cols, float* out) {
@@ -433,6 +514,66 @@ B200_API int b200_nonfinite_flag(const float* a, int64_t rows, int64_t cols, int
   if (blocks > (int64_t)s.sm_count * 8) blocks = (int64_t)s.sm_count * 8;
   nonfinite_kernel<<<(unsigned)blocks, 256, 0, s.stream>>>(a, rows, cols, ld, flag);
   B200_LAUNCH_CHECK();
+  return B200_OK;
+}
+
+// ---- BatchNorm statistics in one pass over the data --------------------------------------
+// Scratch floats the two entry points below need (contiguous (rows, cols) operands).
+B200_API int64_t b200_bn_scratch_floats(int64_t rows, int64_t cols) {
+  if (rows <= 0 || cols <= 0) return 0;
+  int64_t rpc;
+  const int chunks = axis0_plan(rows, cols, true, &rpc);
+  return 2 * (int64_t)chunks * cols;
+}
+
+static int bn_operands_ok(const void* p0, const void* p1, const void* p2, int64_t rows, int64_t cols) {
+  B200_REQUIRE(rows > 0 && cols > 0 && cols % 4 == 0, "the fused BatchNorm kernels need a multiple of 4 columns");
+  B200_REQUIRE(aligned16(p0) && aligned16(p1) && aligned16(p2), "the fused BatchNorm kernels need 16-byte aligned operands");
+  return B200_OK;
+}
+
+// centered[r, c] = x[r, c] + mu[c];  sq_sum[c] = sum_r centered[r, c]^2  (batch_normalization_layer.py:76-86:
+// add_mv, mult_tt, sum_t in one pass; same bits as the three calls).
+B200_API int b200_bn_center_sqsum(const float* x, const float* mu, float* centered, float* sq_sum, int64_t rows,
+                                  int64_t cols, float* scratch, int64_t scratch_floats) {
+  if (int rc = require_ready()) return rc;
+  if (int rc = bn_operands_ok(x, mu, centered, rows, cols)) return rc;
+  const State& s = state();
+  int64_t rpc;
+  const int chunks = axis0_plan(rows, cols, true, &rpc);
+  B200_REQUIRE(chunks == 1 || (scratch && scratch_floats >= (int64_t)chunks * cols), "scratch too small");
+  float* dst = chunks > 1 ? scratch : sq_sum;
+  dim3 grid((unsigned)ceil_div(cols, 128), chunks);
+  bn_colsum_pass1<0><<<grid, dim3(32, 8), 0, s.stream>>>(x, nullptr, mu, centered, rows, cols, rpc, dst, nullptr);
+  B200_LAUNCH_CHECK();
+  if (chunks > 1) {
+    sum_axis0_pass2<<<(unsigned)ceil_div(cols, 256), 256, 0, s.stream>>>(scratch, chunks, cols, sq_sum);
+    B200_LAUNCH_CHECK();
+  }
+  return B200_OK;
+}
+
+// sums[c] = sum_r dout[r, c] * x_hat[r, c];  sums[cols + c] = sum_r dout[r, c]  (:121-133: mult_tt + sum_t and
+// sum_t in one pass over both arrays; same bits as the three calls).
+B200_API int b200_bn_backward_sums(const float* dout, const float* x_hat, float* sums, int64_t rows, int64_t cols,
+                                   float* scratch, int64_t scratch_floats) {
+  if (int rc = require_ready()) return rc;
+  if (int rc = bn_operands_ok(dout, x_hat, sums, rows, cols)) return rc;
+  const State& s = state();
+  int64_t rpc;
+  const int chunks = axis0_plan(rows, cols, true, &rpc);
+  B200_REQUIRE(chunks == 1 || (scratch && scratch_floats >= 2 * (int64_t)chunks * cols), "scratch too small");
+  float* d0 = chunks > 1 ? scratch : sums;
+  float* d1 = chunks > 1 ? scratch + (int64_t)chunks * cols : sums + cols;
+  dim3 grid((unsigned)ceil_div(cols, 128), chunks);
+  bn_colsum_pass1<1><<<grid, dim3(32, 8), 0, s.stream>>>(dout, x_hat, nullptr, nullptr, rows, cols, rpc, d0, d1);
+  B200_LAUNCH_CHECK();
+  if (chunks > 1) {
+    sum_axis0_pass2<<<(unsigned)ceil_div(cols, 256), 256, 0, s.stream>>>(d0, chunks, cols, sums);
+    B200_LAUNCH_CHECK();
+    sum_axis0_pass2<<<(unsigned)ceil_div(cols, 256), 256, 0, s.stream>>>(d1, chunks, cols, sums + cols);
+    B200_LAUNCH_CHECK();
+  }
   return B200_OK;
 }
 

@@ -325,6 +325,41 @@ int b200_col2im_add(const float* col, float* in_deltas, int N, int H, int W, int
 int b200_pool2d_forward(int mode, const float* inputs, float* outputs, float* argmax, int N, int H, int W, int C, int kh, int kw, int pad, int sy, int sx, int oh, int ow);
 int b200_pool2d_backward(int mode, const float* out_deltas, const float* argmax, float* in_deltas, int N, int H, int W, int C, int kh, int kw, int pad, int sy, int sx, int oh, int ow);
 
+/* ---- fused layer arithmetic.  The reference has no such calls: its layers spell this
+ *      arithmetic as chains of Handler calls (brainstorm/layers/highway_layer.py:39-71,
+ *      batch_normalization_layer.py:54-152, fully_connected_layer.py:51-62), one trip
+ *      through memory per call.  Each entry below does the work of the cited chain in one
+ *      pass, rounding every product, sum and quotient separately in the chain's order, so
+ *      the results are the bits the chain gives on this library.  Contiguous operands,
+ *      16-byte aligned, element counts and column counts multiples of 4 (anything else
+ *      is rejected; the host side then runs the reference's chain).
+ *      highway_forward: y = T*(H - x) + x.  highway_backward: dx += (1 - T)*dy,
+ *      dH += T*dy, dT += (H - x)*dy.
+ *      bn_mean: mu_b = s*sum, running = decay*running + one_minus_decay*mu_b (:63-73).
+ *      bn_center_sqsum: centered = x + mu (row vector), sq_sum = column sums of
+ *      centered^2 (:76-86).  bn_sigma: sigma_b = sqrt(inv_m*sq_sum + eps) and the same
+ *      running update (:87-96).  bn_normalize: x_hat = centered / sigma, out =
+ *      x_hat*gamma + beta (:100-104).  bn_backward_sums: sums[0:cols] = column sums of
+ *      dout*x_hat, sums[cols:2 cols] = column sums of dout (:121-133).
+ *      bn_backward_vectors: dgamma += sums[0:cols], dbeta += sums[cols:], vec = [inv_m *
+ *      sums[0:cols], inv_m*sums[cols:], gamma / sigma_b] (3 cols floats, :123-146).
+ *      bn_backward_deltas: in_deltas += ((dout - x_hat*vec0) - vec1)*vec2 (:126-151).
+ *      The column sums use the partial-sum layout of b200_sum_t(axis 0) on a contiguous
+ *      array; scratch of b200_bn_scratch_floats(rows, cols) floats from the caller.
+ *      bias_act: out = f(out + bias) in place, row pitch ld; act 0 sigmoid, 1 tanh,
+ *      2 rel, 3 el, 4 linear (fully_connected_layer.py:61-62). --------------------- */
+int b200_highway_forward(const float* x, const float* H, const float* T, float* y, int64_t n);
+int b200_highway_backward(const float* x, const float* H, const float* T, const float* dy, float* dx, float* dH, float* dT, int64_t n);
+int64_t b200_bn_scratch_floats(int64_t rows, int64_t cols);
+int b200_bn_mean(const float* sum, float s, float decay, float one_minus_decay, float* mu_b, float* running, int64_t cols);
+int b200_bn_center_sqsum(const float* x, const float* mu, float* centered, float* sq_sum, int64_t rows, int64_t cols, float* scratch, int64_t scratch_floats);
+int b200_bn_sigma(const float* sq_sum, float inv_m, float eps, float decay, float one_minus_decay, float* sigma_b, float* running, int64_t cols);
+int b200_bn_normalize(const float* centered, const float* sigma, const float* gamma, const float* beta, float* x_hat, float* out, int64_t rows, int64_t cols);
+int b200_bn_backward_sums(const float* dout, const float* x_hat, float* sums, int64_t rows, int64_t cols, float* scratch, int64_t scratch_floats);
+int b200_bn_backward_vectors(const float* sums, float inv_m, const float* gamma, const float* sigma_b, float* dgamma, float* dbeta, float* vec, int64_t cols);
+int b200_bn_backward_deltas(const float* dout, const float* x_hat, const float* vec, float* in_deltas, int64_t rows, int64_t cols);
+int b200_bias_act(float* out, const float* bias, int64_t rows, int64_t cols, int64_t ld, int act);
+
 /* ---- random: generate_probability_mask :507, fill_gaussian :494;
  *      numpy_handler.py:199,193.  Device-side Philox4x32-10 streams addressed by
  *      (seed, offset); the host-RNG parity mode of the Python handler does not

@@ -55,13 +55,17 @@ def main():
         peer.close()
     for which, build, mode in (
             ('highway_bn', lambda: workloads.highway_bn(batch=32 * world, width=64, classes=7, blocks=2), 'avg'),
+            ('highway_bn_fused', lambda: workloads.highway_bn(batch=32 * world, width=64, classes=7, blocks=2), 'avg'),
             ('lstm', lambda: workloads.lstm(time=6, batch=16 * world, vocab=20, hidden=32), 'local')):
         net, data, stepper = build()
         net.set_handler(H)
         if which == 'lstm':
             fuse_lstm_layers(net)
+        if which == 'highway_bn_fused':
+            from brainstorm_b200.fused_layers import fuse_layers
+            assert len(fuse_layers(net)) == 2 * 4 + 1
         # one network with an all-reduce per layer (what large networks get), one with a single one
-        parallel.OVERLAP_MIN_BYTES = 0 if which == 'highway_bn' else (1 << 40)
+        parallel.OVERLAP_MIN_BYTES = 0 if which.startswith('highway_bn') else (1 << 40)
         data_parallel(net, Comm(), axis0_reduce=mode, peer=True)
         losses = train_steps(net, shard_batch(data, rank, world), stepper(), 3)
         params = net.get('parameters')

@@ -9,7 +9,7 @@ from conftest import needs_reference
 pytestmark = [pytest.mark.gpu, needs_reference]
 
 
-def _pair(builder, fused=False, **kw):
+def _pair(builder, fused=False, prepare=None, **kw):
     import brainstorm as bs
     from brainstorm.handlers import NumpyHandler
     from brainstorm_b200 import B200Handler
@@ -20,6 +20,8 @@ def _pair(builder, fused=False, **kw):
     if fused:
         from brainstorm_b200.fused_lstm import fuse_lstm_layers
         assert len(fuse_lstm_layers(net_gpu)) == kw.get('layers', 2)
+    if prepare is not None:
+        prepare(net_gpu)
     p_cpu = net_cpu.get('parameters')
     p_gpu = net_gpu.get('parameters')
     assert np.array_equal(p_cpu, p_gpu)
@@ -55,10 +57,10 @@ GRAD_TOL, PARAM_TOL, LOSS_TOL = 2e-5, 2e-6, 2e-6
 
 
 def _check_training(builder, steps, grad_tol=GRAD_TOL, param_tol=PARAM_TOL, compare=None, fused=False,
-                    after_first_pass=None, **kw):
+                    after_first_pass=None, prepare=None, **kw):
     compare = compare or _close
     from brainstorm_b200.workloads import train_steps
-    net_cpu, net_gpu, data, stepper = _pair(builder, fused=fused, **kw)
+    net_cpu, net_gpu, data, stepper = _pair(builder, fused=fused, prepare=prepare, **kw)
     # one forward/backward: loss, every gradient
     for net in (net_cpu, net_gpu):
         net.provide_external_data(data)
