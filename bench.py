@@ -328,6 +328,31 @@ def _timed_steps(step, steps, barrier, world, warm=3):
     return _max_over_ranks((time.perf_counter() - t0) / steps, world) * 1e3, loss
 
 
+def _pipelined_ms(net, run, H, host_data, batch, total, warm, barrier, world):
+    """ms per update with the next batch uploaded during the step and the loss read one call
+    late (PrefetchingIterator + defer_loss_readback): `total` minibatches, the first `warm` untimed."""
+    import brainstorm as bs
+    from brainstorm_b200.pipeline import PrefetchingIterator, defer_loss_readback
+    many = {k: np.concatenate([v] * total, axis=1) for k, v in host_data.items()}
+    it = PrefetchingIterator(bs.data_iterators.Minibatches(batch, shuffle=False, **many))
+    deferred = defer_loss_readback(net)
+    barrier()
+    t0, k = None, 0
+    for b in it(handler=H):
+        if k == warm:
+            barrier()
+            t0 = time.perf_counter()
+        net.provide_external_data(b)
+        run()
+        net.get_loss_values()
+        k += 1
+    deferred.flush()
+    barrier()
+    ms = _max_over_ranks((time.perf_counter() - t0) / (k - warm), world) * 1e3
+    deferred.restore()
+    return ms
+
+
 def lstm_training(H, world, rank, steps, barrier, lib):
     """Second half of the metric: training sequences per second of the character LSTM
     (time 100, batch 128 per GPU, 205 symbols, 2 x 1000 units, SoftmaxCE, SGD) through the
@@ -340,7 +365,6 @@ def lstm_training(H, world, rank, steps, barrier, lib):
         return {'unavailable': why}
     from brainstorm_b200 import workloads
     from brainstorm_b200.fused_lstm import fuse_lstm_layers
-    from brainstorm_b200.pipeline import PrefetchingIterator, defer_loss_readback
     T, B = 100, 128
     net, data, stepper = workloads.lstm(time=T, batch=B, data_seed=rank)
     pinned = {}
@@ -374,25 +398,7 @@ def lstm_training(H, world, rank, steps, barrier, lib):
     out['vs_n1'] = round(out['sequences_per_s'] / out['n1_sequences_per_s'], 3)
     out['loss'] = round(loss, 4)
     # the same updates with the next batch uploaded during the step and the loss read one call late
-    import brainstorm as bs
-    n = steps + 3
-    many = {k: np.concatenate([v] * n, axis=1) for k, v in data.items()}
-    it = PrefetchingIterator(bs.data_iterators.Minibatches(B, shuffle=False, **many))
-    deferred = defer_loss_readback(net)
-    barrier()
-    t0, k = None, 0
-    for batch in it(handler=H):
-        if k == 3:
-            barrier()
-            t0 = time.perf_counter()
-        net.provide_external_data(batch)
-        st.run()
-        net.get_loss_values()
-        k += 1
-    deferred.flush()
-    barrier()
-    out['pipelined_ms'] = round(_max_over_ranks((time.perf_counter() - t0) / (k - 3), world) * 1e3, 3)
-    deferred.restore()
+    out['pipelined_ms'] = round(_pipelined_ms(net, lambda: st.run(), H, data, B, steps + 3, 3, barrier, world), 3)
     out['h2d_bytes_per_step'] = int(sum(v.nbytes for v in pinned.values()))
     return out
 
@@ -477,6 +483,8 @@ def other_training(name, H, world, rank, barrier, lib, new_event, elapsed):
         ms, _ = _timed_steps(step, steps, barrier, world)
         out['fused_layers'] = {'ms_per_step': round(ms, 3), 'samples_per_s': round(global_batch / ms * 1e3, 1),
                                'launches_per_step': int((lib.b200_launch_count() - l0) // (steps + 3))}
+        ms = _pipelined_ms(net, lambda: st.run(), H, host_data, data['default'].shape[1], steps + 3, 3, barrier, world)
+        out['fused_layers']['pipelined_ms_per_step'] = round(ms, 3)
     if name == 'mlp' or world > 1:
         gs = GraphedStepper(stepper(), eager_steps=1)
         gs.start(net)
@@ -487,27 +495,7 @@ def other_training(name, H, world, rank, barrier, lib, new_event, elapsed):
             out['recorded_samples_per_s'] = round(global_batch / ms * 1e3, 1)
         if name == 'mlp' and gs._step is not None:
             # the recorded step with the next batch uploaded during the step and the loss read one call late
-            import brainstorm as bs
-            from brainstorm_b200.pipeline import PrefetchingIterator, defer_loss_readback
-            n = 200
-            batch = data['default'].shape[1]
-            many = {k: np.concatenate([v] * n, axis=1) for k, v in host_data.items()}
-            it = PrefetchingIterator(bs.data_iterators.Minibatches(batch, shuffle=False, **many))
-            deferred = defer_loss_readback(net)
-            barrier()
-            t0, k = None, 0
-            for b in it(handler=H):
-                if k == 20:
-                    barrier()
-                    t0 = time.perf_counter()
-                net.provide_external_data(b)
-                st.run()
-                net.get_loss_values()
-                k += 1
-            deferred.flush()
-            barrier()
-            ms = _max_over_ranks((time.perf_counter() - t0) / (k - 20), world) * 1e3
-            deferred.restore()
+            ms = _pipelined_ms(net, lambda: st.run(), H, host_data, data['default'].shape[1], 200, 20, barrier, world)
             out['recorded_pipelined_ms_per_step'] = round(ms, 3)
             out['recorded_pipelined_samples_per_s'] = round(global_batch / ms * 1e3, 1)
         gs.invalidate()
