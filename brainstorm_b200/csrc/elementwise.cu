@@ -434,10 +434,50 @@ bias_act_vec(float* out, const float* bias, int64_t rows, int cols4, int64_t ld,
   }
 }
 
+// The same for rows without a pitch: the flat walk of ew_flat_vec, the bias vector read through L1.
+template <class F, bool STREAM>
+__global__ void __launch_bounds__(1024)
+bias_act_flat(float* out, const float* bias, int64_t nvec, int cols4, Params p) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t base = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; base < nvec; base += stride * EW_UNROLL) {
+    float4 a[EW_UNROLL];
+#pragma unroll
+    for (int u = 0; u < EW_UNROLL; ++u) {
+      const int64_t i = base + u * stride;
+      a[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (i < nvec) a[u] = ld4<STREAM>(out + 4 * i);
+    }
+#pragma unroll
+    for (int u = 0; u < EW_UNROLL; ++u) {
+      const int64_t i = base + u * stride;
+      if (i >= nvec) continue;
+      const float4 b = *reinterpret_cast<const float4*>(bias + 4 * (i % cols4));
+      float4 v;
+      v.x = F::apply(__fadd_rn(a[u].x, b.x), 0.f, 0.f, p);
+      v.y = F::apply(__fadd_rn(a[u].y, b.y), 0.f, 0.f, p);
+      v.z = F::apply(__fadd_rn(a[u].z, b.z), 0.f, 0.f, p);
+      v.w = F::apply(__fadd_rn(a[u].w, b.w), 0.f, 0.f, p);
+      st4<STREAM>(out + 4 * i, v);
+    }
+  }
+}
+
 template <class F>
 static int launch_bias_act(float* out, const float* bias, int64_t rows, int64_t cols, int64_t ld) {
   const State& s = state();
   const int cols4 = (int)(cols / 4);
+  if (ld == cols) {
+    const bool tuned = s.ew_threads != 1024 || s.ew_blocks_per_sm != 32;
+    const int threads = (!tuned && F::LAUNCH == 1) ? 512 : s.ew_threads;
+    const int bps = (!tuned && F::LAUNCH == 2) ? 16 : 0;
+    const int64_t nvec = rows * cols4;
+    if (nvec * 4 >= STREAM_MIN_ELEMS)
+      bias_act_flat<F, true><<<ew_grid(nvec, threads, bps), threads, 0, s.stream>>>(out, bias, nvec, cols4, Params{0.f, 0.f});
+    else
+      bias_act_flat<F, false><<<ew_grid(nvec, threads, bps), threads, 0, s.stream>>>(out, bias, nvec, cols4, Params{0.f, 0.f});
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+  }
   const int tx = cols4 >= 256 ? 256 : (cols4 >= 128 ? 128 : (cols4 >= 64 ? 64 : 32));
   int ty = s.ew_threads / tx;
   if (ty < 1) ty = 1;

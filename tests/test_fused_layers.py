@@ -97,3 +97,26 @@ def test_fused_layers_in_a_recorded_step():
     got = train_steps(fused, data, GraphedStepper(bs.training.SgdStepper(learning_rate=0.01)), 5)
     assert want == got
     assert np.array_equal(plain.get('parameters'), fused.get('parameters'))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize('act', ['sigmoid', 'tanh', 'rel', 'el', 'linear'])
+@pytest.mark.parametrize('rows,cols,ld', [(1, 4, 4), (37, 64, 64), (37, 64, 72), (513, 1028, 1028), (300, 12, 40)])
+def test_bias_act_gives_the_bits_of_add_mv_then_the_activation(act, rows, cols, ld):
+    """b200_bias_act against the two handler calls it replaces (fully_connected_layer.py:61-62),
+    on rows with and without a pitch."""
+    from brainstorm_b200 import B200Handler
+    from brainstorm_b200._lib import lib, check
+    from brainstorm_b200.fused_layers import _ACT
+    H = B200Handler()
+    rs = np.random.RandomState(rows * 131 + cols)
+    x = (3 * rs.randn(rows, ld)).astype(np.float32)
+    bias = rs.randn(cols).astype(np.float32)
+    want = H.create_from_numpy(x)[:, :cols]
+    H.add_mv(want, H.create_from_numpy(bias.reshape(1, cols)), want)
+    H.inplace_act_func[act](want)
+    got = H.create_from_numpy(x)
+    check(lib.b200_bias_act(got.ptr, H.create_from_numpy(bias).ptr, rows, cols, ld, _ACT[act]))
+    got = H.get_numpy_copy(got)
+    assert np.array_equal(got[:, :cols], H.get_numpy_copy(want))
+    assert np.array_equal(got[:, cols:], x[:, cols:])            # the padding of pitched rows is untouched
