@@ -475,10 +475,15 @@ def other_training(name, H, world, rank, barrier, lib, new_event, elapsed):
         out['host_queue_ms'] = round(_max_over_ranks((time.perf_counter() - t0), world) * 1e3, 3)
         H.synchronize()
     if name == 'highway_bn':
-        # the same network with the Highway, BatchNorm and FullyConnected layers in their fused forms (same bits);
-        # the recorded step below runs them too
+        # the same network with the Highway, BatchNorm and FullyConnected layers in their fused forms and the
+        # stepper's update as one call (same bits); the recorded step below runs them too
         from brainstorm_b200.fused_layers import fuse_layers
+        from brainstorm_b200.steppers import FusedSgdStepper
         fuse_layers(net)
+        lr = st.learning_rate
+        stepper = lambda: FusedSgdStepper(learning_rate=lr)          # the update as one kernel, same bits
+        st = stepper()
+        st.start(net)
         l0 = lib.b200_launch_count()
         ms, _ = _timed_steps(step, steps, barrier, world)
         out['fused_layers'] = {'ms_per_step': round(ms, 3), 'samples_per_s': round(global_batch / ms * 1e3, 1),

@@ -120,3 +120,29 @@ def test_bias_act_gives_the_bits_of_add_mv_then_the_activation(act, rows, cols, 
     got = H.get_numpy_copy(got)
     assert np.array_equal(got[:, :cols], H.get_numpy_copy(want))
     assert np.array_equal(got[:, cols:], x[:, cols:])            # the padding of pitched rows is untouched
+
+
+def _sgd_pair(make_handler):
+    import brainstorm as bs
+    from brainstorm_b200 import workloads
+    from brainstorm_b200.steppers import FusedSgdStepper
+    from brainstorm_b200.workloads import train_steps
+    out = []
+    for cls in (bs.training.SgdStepper, FusedSgdStepper):
+        net, data, _ = workloads.highway_bn(batch=24, width=16, classes=5, blocks=2)
+        net.set_handler(make_handler())
+        losses = train_steps(net, data, cls(learning_rate=0.07), 4)
+        out.append((losses, net.get('parameters')))
+    assert out[0][0] == out[1][0]
+    assert np.array_equal(out[0][1], out[1][1])
+
+
+def test_fused_sgd_stepper_gives_the_bits_of_sgd_stepper_on_numpy_handler():
+    from brainstorm.handlers import NumpyHandler
+    _sgd_pair(lambda: NumpyHandler(np.float32))
+
+
+@pytest.mark.gpu
+def test_fused_sgd_stepper_gives_the_bits_of_sgd_stepper():
+    from brainstorm_b200 import B200Handler
+    _sgd_pair(lambda: B200Handler())
