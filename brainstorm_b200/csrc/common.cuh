@@ -64,6 +64,7 @@ struct State {
   int ew_blocks_per_sm = 32;
   int ew_threads = 1024;
   int red_blocks_per_sm = 8;   // pass-1 blocks per SM of the two-pass sums
+  int axis0_fold = 1;          // column sums: the last pass-1 block of a column group does pass 2 (0: a launch of its own)
   int gemm_path = 0;  // 0 = auto, 1 = force SIMT, 2 = force tensor-core
   int gemm_bn = 0;    // 0 = auto, else forced tile width (32/64/128/256)
   int use_pdl = 1;    // programmatic dependent launch inside the LSTM time loops

@@ -64,13 +64,55 @@ sum_all_pass2(const float* partial, int count, float* out) {
 }
 
 // ---- sum over axis 0 (column sums) ----------------------------------------------------
+// Pass 2 without a second launch.  Every block of a column group (blockIdx.x) takes a ticket
+// after its partial sums are visible; the block that draws the last ticket adds the group's
+// partials in the fixed order of sum_axis0_pass2 (so the bits do not depend on which block
+// that is) and hands the ticket counter back at zero.  The counters belong to the library,
+// one set per library stream: calls on one stream are ordered, and the two streams never
+// share a set.
+constexpr int AXIS0_TICKET_SLOTS = 4096;     // column groups per call that can use the folded form
+__device__ unsigned g_axis0_tickets[2][AXIS0_TICKET_SLOTS];
+
+// Called by all 256 threads of a 32 x 8 block after they have stored their partials.
+// `width` columns from `col0` belong to this block.
+__device__ __forceinline__ void axis0_fold_pass2(unsigned* tickets, const float* partial, const float* partial2, float* out,
+                                                 float* out2, int64_t cols, int64_t col0, int width) {
+  __shared__ int is_last;
+  __threadfence();
+  __syncthreads();
+  const int t = threadIdx.y * 32 + threadIdx.x;
+  if (t == 0) {
+    const unsigned drawn = atomicAdd(&tickets[blockIdx.x], 1u);
+    is_last = drawn == gridDim.y - 1;
+    if (is_last) tickets[blockIdx.x] = 0;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  const int chunks = (int)gridDim.y;
+  for (int j = t; j < width * (partial2 ? 2 : 1); j += 256) {
+    const float* p = j < width ? partial : partial2;
+    float* o = j < width ? out : out2;
+    const int64_t c = col0 + (j < width ? j : j - width);
+    if (c >= cols) continue;
+    float s0 = 0.f, s1 = 0.f;
+    int k = 0;
+    for (; k + 1 < chunks; k += 2) {
+      s0 += __ldcg(p + (int64_t)k * cols + c);
+      s1 += __ldcg(p + (int64_t)(k + 1) * cols + c);
+    }
+    if (k < chunks) s0 += __ldcg(p + (int64_t)k * cols + c);
+    o[c] = s0 + s1;
+  }
+}
+
 // Block = 32 x 8 threads.  VEC: a thread owns 4 adjacent columns (block covers
 // 128 columns), else 1 column (block covers 32).  blockIdx.y selects a chunk of
 // rows; the block's result goes to dst[blockIdx.y * cols + c].
 template <bool VEC>
 __global__ void __launch_bounds__(256)
 sum_axis0_pass1(const float* a, int64_t rows, int64_t cols, int64_t ld, int64_t rows_per_chunk,
-                float* dst) {
+                float* dst, float* out, unsigned* tickets) {
   constexpr int W = VEC ? 4 : 1;
   __shared__ float smem[8][32 * W + 1];
   const int tx = threadIdx.x, ty = threadIdx.y;
@@ -123,6 +165,7 @@ sum_axis0_pass1(const float* a, int64_t rows, int64_t cols, int64_t ld, int64_t 
     const int64_t cc = (int64_t)blockIdx.x * 32 * W + j;
     if (cc < cols) dst[(int64_t)blockIdx.y * cols + cc] = s;
   }
+  if (tickets) axis0_fold_pass2(tickets, dst, nullptr, out, nullptr, cols, (int64_t)blockIdx.x * 32 * W, 32 * W);
 }
 
 // ---- column sums with the producing elementwise step folded in (BatchNorm) -------------
@@ -137,7 +180,7 @@ sum_axis0_pass1(const float* a, int64_t rows, int64_t cols, int64_t ld, int64_t 
 template <int MODE>
 __global__ void __launch_bounds__(256)
 bn_colsum_pass1(const float* a, const float* b, const float* vec, float* centered, int64_t rows, int64_t cols,
-                int64_t rows_per_chunk, float* dst, float* dst2) {
+                int64_t rows_per_chunk, float* dst, float* dst2, float* out, unsigned* tickets) {
   __shared__ float smem[8][32 * 4 + 1];
   const int tx = threadIdx.x, ty = threadIdx.y;
   const int64_t c = ((int64_t)blockIdx.x * 32 + tx) * 4;
@@ -194,16 +237,19 @@ bn_colsum_pass1(const float* a, const float* b, const float* vec, float* centere
       smem[ty][tx * 4 + w] = ((acc[s][0][w] + acc[s][1][w]) + (acc[s][2][w] + acc[s][3][w])) +
                              ((acc[s][4][w] + acc[s][5][w]) + (acc[s][6][w] + acc[s][7][w]));
     __syncthreads();
-    float* out = s == 0 ? dst : dst2;
+    float* part = s == 0 ? dst : dst2;
     for (int j = ty * 32 + tx; j < 32 * 4; j += 256) {
       float t = 0.f;
 #pragma unroll
       for (int k = 0; k < 8; ++k) t += smem[k][j];
       const int64_t cc = (int64_t)blockIdx.x * 32 * 4 + j;
-      if (cc < cols) out[(int64_t)blockIdx.y * cols + cc] = t;
+      if (cc < cols) part[(int64_t)blockIdx.y * cols + cc] = t;
     }
     __syncthreads();
   }
+  if (tickets)
+    axis0_fold_pass2(tickets, dst, MODE == 1 ? dst2 : nullptr, out, MODE == 1 ? out + cols : nullptr, cols,
+                     (int64_t)blockIdx.x * 128, 128);
 }
 
 // out[c] = sum over chunks of partial[chunk * cols + c], fixed order
@@ -355,6 +401,8 @@ nonfinite_kernel(const float* a, int64_t rows, int64_t cols, int64_t ld, int* fl
 // blocks handed out dynamically even out what the memory system gives each SM; a grid of
 // exactly one resident wave was measured slower (column sums 6.20 -> 5.97 TB/s, sum over
 // everything 6.45 -> 6.31), because every SM then waits for the slowest block.
+unsigned* axis0_tickets(int64_t groups);
+
 static int axis0_plan(int64_t rows, int64_t cols, bool vec, int64_t* rows_per_chunk) {
   const State& s = state();
   const int64_t gx = ceil_div(cols, vec ? 128 : 32);
@@ -440,15 +488,17 @@ B200_API int b200_sum_t(const float* a, int64_t rows, int64_t cols, int64_t ld, 
     int64_t rpc;
     const int chunks = axis0_plan(rows, cols, vec_layout, &rpc);
     float* dst = chunks > 1 ? scratch : out;
+    const int64_t groups = ceil_div(cols, vec ? 128 : 32);
+    unsigned* tickets = chunks > 1 ? axis0_tickets(groups) : nullptr;
     if (vec) {
-      dim3 grid((unsigned)ceil_div(cols, 128), chunks);
-      sum_axis0_pass1<true><<<grid, dim3(32, 8), 0, s.stream>>>(a, rows, cols, ld, rpc, dst);
+      dim3 grid((unsigned)groups, chunks);
+      sum_axis0_pass1<true><<<grid, dim3(32, 8), 0, s.stream>>>(a, rows, cols, ld, rpc, dst, out, tickets);
     } else {
-      dim3 grid((unsigned)ceil_div(cols, 32), chunks);
-      sum_axis0_pass1<false><<<grid, dim3(32, 8), 0, s.stream>>>(a, rows, cols, ld, rpc, dst);
+      dim3 grid((unsigned)groups, chunks);
+      sum_axis0_pass1<false><<<grid, dim3(32, 8), 0, s.stream>>>(a, rows, cols, ld, rpc, dst, out, tickets);
     }
     B200_LAUNCH_CHECK();
-    if (chunks > 1) {
+    if (chunks > 1 && !tickets) {
       sum_axis0_pass2<<<(unsigned)ceil_div(cols, 256), 256, 0, s.stream>>>(scratch, chunks, cols, out);
       B200_LAUNCH_CHECK();
     }
@@ -544,9 +594,10 @@ B200_API int b200_bn_center_sqsum(const float* x, const float* mu, float* center
   B200_REQUIRE(chunks == 1 || (scratch && scratch_floats >= (int64_t)chunks * cols), "scratch too small");
   float* dst = chunks > 1 ? scratch : sq_sum;
   dim3 grid((unsigned)ceil_div(cols, 128), chunks);
-  bn_colsum_pass1<0><<<grid, dim3(32, 8), 0, s.stream>>>(x, nullptr, mu, centered, rows, cols, rpc, dst, nullptr);
+  unsigned* tickets = chunks > 1 ? axis0_tickets(grid.x) : nullptr;
+  bn_colsum_pass1<0><<<grid, dim3(32, 8), 0, s.stream>>>(x, nullptr, mu, centered, rows, cols, rpc, dst, nullptr, sq_sum, tickets);
   B200_LAUNCH_CHECK();
-  if (chunks > 1) {
+  if (chunks > 1 && !tickets) {
     sum_axis0_pass2<<<(unsigned)ceil_div(cols, 256), 256, 0, s.stream>>>(scratch, chunks, cols, sq_sum);
     B200_LAUNCH_CHECK();
   }
@@ -566,9 +617,10 @@ B200_API int b200_bn_backward_sums(const float* dout, const float* x_hat, float*
   float* d0 = chunks > 1 ? scratch : sums;
   float* d1 = chunks > 1 ? scratch + (int64_t)chunks * cols : sums + cols;
   dim3 grid((unsigned)ceil_div(cols, 128), chunks);
-  bn_colsum_pass1<1><<<grid, dim3(32, 8), 0, s.stream>>>(dout, x_hat, nullptr, nullptr, rows, cols, rpc, d0, d1);
+  unsigned* tickets = chunks > 1 ? axis0_tickets(grid.x) : nullptr;
+  bn_colsum_pass1<1><<<grid, dim3(32, 8), 0, s.stream>>>(dout, x_hat, nullptr, nullptr, rows, cols, rpc, d0, d1, sums, tickets);
   B200_LAUNCH_CHECK();
-  if (chunks > 1) {
+  if (chunks > 1 && !tickets) {
     sum_axis0_pass2<<<(unsigned)ceil_div(cols, 256), 256, 0, s.stream>>>(d0, chunks, cols, sums);
     B200_LAUNCH_CHECK();
     sum_axis0_pass2<<<(unsigned)ceil_div(cols, 256), 256, 0, s.stream>>>(d1, chunks, cols, sums + cols);
@@ -593,6 +645,7 @@ namespace b200 {
 // address is looked up once per device, with that device current, when b200_init binds
 // the process to its GPU; b200_sum_t_static only reads it here afterwards.
 static float* g_static_scratch_ptr[64] = {nullptr};
+static unsigned* g_axis0_tickets_ptr[64] = {nullptr};    // the ticket counters of the folded second pass, same rule
 
 int static_scratch_setup() {
   int dev = -1;
@@ -604,7 +657,23 @@ int static_scratch_setup() {
     B200_REQUIRE(p != nullptr, "cudaGetSymbolAddress returned a NULL address");
     g_static_scratch_ptr[dev] = p;
   }
+  if (g_axis0_tickets_ptr[dev] == nullptr) {
+    unsigned* t = nullptr;
+    B200_CUDA(cudaGetSymbolAddress((void**)&t, g_axis0_tickets));
+    B200_REQUIRE(t != nullptr, "cudaGetSymbolAddress returned a NULL address");
+    g_axis0_tickets_ptr[dev] = t;
+  }
   return B200_OK;
+}
+
+// The ticket counters for a column-sum launch of `groups` column groups on the current stream,
+// or NULL when the second pass has to be a launch of its own (more groups than counters, the
+// folded form switched off, or no address yet).
+unsigned* axis0_tickets(int64_t groups) {
+  const State& s = state();
+  if (!s.axis0_fold || groups > AXIS0_TICKET_SLOTS || s.device < 0 || s.device >= 64) return nullptr;
+  unsigned* base = g_axis0_tickets_ptr[s.device];
+  return base ? base + (s.stream_index ? AXIS0_TICKET_SLOTS : 0) : nullptr;
 }
 }  // namespace b200
 

@@ -49,7 +49,10 @@ int b200_device_info(int* device, int* sm_count, uint64_t* free_bytes, uint64_t*
  *    drains into fp32 registers (1, 2, 4 or 8; 0 = the default, 2): shorter chunks lose
  *    less to the tensor core's truncating accumulation and cost a little throughput;
  * 10: pass-1 blocks per SM of the two-pass sums (default 8; changes what
- *    b200_sum_t_scratch_floats returns). */
+ *    b200_sum_t_scratch_floats returns);
+ * 11: column sums (axis 0) run their second pass inside the first kernel: the block that
+ *    finishes a column group last adds the group's partial sums, in the same fixed order
+ *    (default 1; 0 = a second launch; same bits either way). */
 int b200_set_tuning(int key, int value);
 uint64_t b200_stream(void);                            /* the main stream (a cudaStream_t) */
 /* A second compute stream, for work that may run beside the main stream's (a stack of
