@@ -702,6 +702,7 @@ def run_b200(args):
     e_start, e_stop = new_event(), new_event()
     sampler = ClockSampler(local_rank) if rank == 0 else None
     launches0 = lib.b200_launch_count()
+    waits0 = comm.peer_wait_stats() if peer_ok else None
     barrier()
     t0 = time.time()
     check(lib.b200_event_record(e_start))
@@ -710,6 +711,12 @@ def run_b200(args):
     check(lib.b200_event_record(e_stop))
     barrier()
     t1 = time.time()
+    axis0_wait_us = None
+    if waits0 is not None:
+        # how long the exchange inside sum_t(axis=0) waited for the slowest rank: [least, most] patient rank
+        calls, waited = comm.peer_wait_stats()
+        mine = (waited - waits0[1]) / max(1, calls - waits0[0]) * 1e6
+        axis0_wait_us = [round(-_max_over_ranks(-mine, world), 1), round(_max_over_ranks(mine, world), 1)]
     launches = lib.b200_launch_count() - launches0
     total_ms = _max_over_ranks(elapsed(e_start, e_stop), world)
     clocks = sampler.stop(t0, t1) if sampler else None
@@ -725,7 +732,8 @@ def run_b200(args):
         return finish({'metric': METRIC, 'value': round(value, 1), 'unit': UNIT, 'n_gpus': world,
                        'steps': args.steps, 'ms_per_step': round(ms_per_step, 4),
                        'config': {'workload': 'handler op suite only, (%d, %d)' % (ROWS, COLS)},
-                       'gpu_launches': int(launches), 'peer_ok': peer_ok, 'ops_ms_gbs': ops})
+                       'gpu_launches': int(launches), 'peer_ok': peer_ok, 'axis0_exchange_wait_us': axis0_wait_us,
+                       'ops_ms_gbs': ops})
     # ---- end to end: host buffers in, results out, every step
     e2e_steps = max(2, min(args.steps, 4))
     results = [np.empty((1, COLS), np.float32), np.empty((ROWS, 1), np.float32),
@@ -819,6 +827,7 @@ def run_b200(args):
             'gemm': gemm,
             'other_training': others,
             'peer_ok': peer_ok,
+            'axis0_exchange_wait_us': axis0_wait_us,
             'lstm': lstm,
         }
     finish(line)

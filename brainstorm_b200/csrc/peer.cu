@@ -39,6 +39,7 @@ constexpr int PEER_MAX_FLOATS = 65536;                  // per call: 256 KiB per
 constexpr size_t PEER_SLOT_BYTES = (size_t)PEER_MAX_FLOATS * sizeof(float);
 constexpr size_t PEER_COUNTER_OFFSET = 2 * PEER_SLOT_BYTES;
 constexpr size_t PEER_CALLS_OFFSET = PEER_COUNTER_OFFSET + 128;  // this rank's own call counter (the epoch)
+constexpr size_t PEER_WAITED_OFFSET = PEER_CALLS_OFFSET + 8;      // nanoseconds this rank's calls have spent waiting for the others
 constexpr size_t PEER_WINDOW_BYTES = PEER_COUNTER_OFFSET + 256;   // counters: PEER_MAX_RANKS x 8 bytes, the call counter, padding
 
 struct PeerState {
@@ -66,6 +67,7 @@ peer_allreduce_kernel(PeerArgs a, const float* src, float* dst, int n, int avera
                       int* error_flag, unsigned spin_limit) {
   __shared__ int timed_out;
   __shared__ unsigned long long epoch_shared;
+  __shared__ const float* slots[PEER_MAX_RANKS];     // every rank's slot of this epoch's parity
   // The epoch is this rank's call counter.  It lives in the window, not in an argument, so
   // that a call recorded into a graph takes the next epoch on every replay.
   if (threadIdx.x == 0) {
@@ -78,13 +80,24 @@ peer_allreduce_kernel(PeerArgs a, const float* src, float* dst, int n, int avera
   const int slot = (int)(epoch & 1);
   float* mine = reinterpret_cast<float*>(a.window[a.rank] + slot * PEER_SLOT_BYTES);
   if (threadIdx.x == 0) timed_out = 0;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) mine[i] = src[i];
+  if (threadIdx.x < a.world)
+    slots[threadIdx.x] = reinterpret_cast<const float*>(a.window[threadIdx.x] + slot * PEER_SLOT_BYTES);
+  // 128-bit accesses when the caller's arrays allow them (the slots always do)
+  const bool vec = (n & 3) == 0 && ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0;
+  if (vec) {
+    for (int i = threadIdx.x; i < (n >> 2); i += blockDim.x)
+      reinterpret_cast<float4*>(mine)[i] = reinterpret_cast<const float4*>(src)[i];
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) mine[i] = src[i];
+  }
   __threadfence_system();     // the slot is written before the epoch is published
   __syncthreads();
   if (threadIdx.x < a.world) {
     unsigned long long* counters = reinterpret_cast<unsigned long long*>(a.window[threadIdx.x] + PEER_COUNTER_OFFSET);
     st_release_sys(counters + a.rank, epoch);
   }
+  unsigned long long wait_begin = 0;
+  if (threadIdx.x == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(wait_begin));
   if (threadIdx.x < a.world) {
     const unsigned long long* counters =
         reinterpret_cast<const unsigned long long*>(a.window[a.rank] + PEER_COUNTER_OFFSET);
@@ -98,17 +111,54 @@ peer_allreduce_kernel(PeerArgs a, const float* src, float* dst, int n, int avera
     if (!seen) timed_out = 1;
   }
   __syncthreads();
+  if (threadIdx.x == 0) {     // how long the slowest rank kept this one waiting (b200_peer_wait_stats)
+    unsigned long long wait_end;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(wait_end));
+    *reinterpret_cast<unsigned long long*>(a.window[a.rank] + PEER_WAITED_OFFSET) += wait_end - wait_begin;
+  }
   if (timed_out) {
     if (threadIdx.x == 0 && error_flag) *error_flag = 1;
     return;                   // dst is left as it was; the host reports the flag
   }
+  // The ranks' slots are read eight at a time: the loads of a batch are all issued before the first
+  // sum needs one, so a batch costs one trip over NVLink, not one per rank.  The sums run in rank order.
   const float scale = average ? 1.0f / (float)a.world : 1.0f;
+  constexpr int BATCH = 8;
+  if (vec) {
+    const int nv = n >> 2;
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int r0 = 0; r0 < a.world; r0 += BATCH) {
+        float4 v[BATCH];
+#pragma unroll
+        for (int k = 0; k < BATCH; ++k)
+          if (r0 + k < a.world) v[k] = __ldcv(reinterpret_cast<const float4*>(slots[r0 + k]) + i);   // not cached: written by another GPU
+#pragma unroll
+        for (int k = 0; k < BATCH; ++k) {
+          if (r0 + k >= a.world) continue;
+          if (r0 + k == 0) acc = v[k];
+          else acc = make_float4(__fadd_rn(acc.x, v[k].x), __fadd_rn(acc.y, v[k].y), __fadd_rn(acc.z, v[k].z),
+                                 __fadd_rn(acc.w, v[k].w));
+        }
+      }
+      if (average) acc = make_float4(__fmul_rn(acc.x, scale), __fmul_rn(acc.y, scale), __fmul_rn(acc.z, scale),
+                                     __fmul_rn(acc.w, scale));
+      reinterpret_cast<float4*>(dst)[i] = acc;
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     float acc = 0.f;
-    for (int r = 0; r < a.world; ++r) {
-      const float* theirs = reinterpret_cast<const float*>(a.window[r] + slot * PEER_SLOT_BYTES);
-      const float v = __ldcv(theirs + i);     // not cached: written by another GPU
-      acc = (r == 0) ? v : __fadd_rn(acc, v);
+    for (int r0 = 0; r0 < a.world; r0 += BATCH) {
+      float v[BATCH];
+#pragma unroll
+      for (int k = 0; k < BATCH; ++k)
+        if (r0 + k < a.world) v[k] = __ldcv(slots[r0 + k] + i);
+#pragma unroll
+      for (int k = 0; k < BATCH; ++k) {
+        if (r0 + k >= a.world) continue;
+        acc = (r0 + k == 0) ? v[k] : __fadd_rn(acc, v[k]);
+      }
     }
     dst[i] = average ? __fmul_rn(acc, scale) : acc;
   }
@@ -187,6 +237,19 @@ B200_API int b200_peer_setup(int rank, int world, const uint64_t* windows) {
   g_peer.world = world;
   g_peer.disabled = false;
   for (int r = 0; r < world; ++r) g_peer.window[r] = (uint8_t*)(uintptr_t)windows[r];
+  return B200_OK;
+}
+
+// Calls made since b200_peer_setup and the time they spent between publishing their epoch and seeing
+// everybody else's (the other ranks' lateness plus one trip over NVLink).  Synchronises.
+B200_API int b200_peer_wait_stats(uint64_t* calls, uint64_t* waited_ns) {
+  if (int rc = require_ready()) return rc;
+  B200_REQUIRE(g_peer.world > 0 && calls != nullptr && waited_ns != nullptr, "no peer registration or NULL argument");
+  B200_CUDA(cudaStreamSynchronize(state().stream));
+  unsigned long long both[2] = {0, 0};
+  B200_CUDA(cudaMemcpy(both, g_peer.window[g_peer.rank] + PEER_CALLS_OFFSET, sizeof(both), cudaMemcpyDeviceToHost));
+  *calls = both[0];
+  *waited_ns = both[1];
   return B200_OK;
 }
 

@@ -157,6 +157,15 @@ class Comm(object):
             return False
         return True
 
+    def peer_wait_stats(self):
+        """(calls, seconds): the peer all-reduces of this rank since ``enable_peer`` and the time
+        their kernels spent waiting for the other ranks' values.  Synchronises."""
+        import ctypes
+        from ._lib import lib, check
+        calls, waited = ctypes.c_uint64(), ctypes.c_uint64()
+        check(lib.b200_peer_wait_stats(ctypes.byref(calls), ctypes.byref(waited)))
+        return calls.value, waited.value * 1e-9
+
     def _peer_allreduce(self, arr, op):
         from ._lib import lib, check
         check(lib.b200_peer_allreduce(arr.ptr, arr.ptr, arr.size, 1 if op == 'avg' else 0))

@@ -140,7 +140,10 @@ int b200_graph_destroy(uint64_t graph);
  * registered again (the ranks' call counters no longer agree).  b200_peer_setup clears this
  * rank's arrival counters: put a host barrier over all ranks between it and the first
  * b200_peer_allreduce.  b200_peer_window_release gives back a window that never reached
- * b200_peer_setup (own != 0: allocated here; 0: opened from a handle).  The reference has
+ * b200_peer_setup (own != 0: allocated here; 0: opened from a handle).
+ * b200_peer_wait_stats reports the calls made since b200_peer_setup and the nanoseconds
+ * they spent between publishing their values and seeing every other rank's (how late
+ * the slowest rank was, plus one trip over NVLink); it synchronises.  The reference has
  * no counterpart (it has no multi-GPU code). */
 uint64_t b200_peer_window_bytes(void);
 int b200_peer_max_floats(void);
@@ -150,6 +153,7 @@ int b200_peer_window_release(uint64_t ptr, int own);
 int b200_peer_setup(int rank, int world, const uint64_t* windows);
 int b200_peer_enabled(void);
 int b200_peer_allreduce(const float* src, float* dst, int n, int average);
+int b200_peer_wait_stats(uint64_t* calls, uint64_t* waited_ns);
 int b200_peer_teardown(void);
 
 /* ---- all-reduce of device arrays over NCCL -----------------------------------
