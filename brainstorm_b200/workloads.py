@@ -110,6 +110,32 @@ def highway_bn(batch=8192, width=4096, classes=1000, blocks=10, seed=42, data_se
     return net, data, stepper
 
 
+def cifar10_cnn(batch=100, seed=42, data_seed=0):
+    """The convolutional network of the reference's examples/cifar10_cnn.py:28-46 (three 5x5
+    convolutions with 3x3 / stride-2 max pooling, two FullyConnected layers, momentum SGD,
+    minibatches of 100) on seeded stand-ins for normalised 32 x 32 x 3 images."""
+    bs = _bs()
+    bs.global_rnd.set_seed(seed)
+    inp, fc = bs.tools.get_in_out_layers('classification', (32, 32, 3), 10)
+    (inp >>
+     bs.layers.Convolution2D(32, kernel_size=(5, 5), padding=2, name='Conv1') >>
+     bs.layers.Pooling2D(type='max', kernel_size=(3, 3), stride=(2, 2)) >>
+     bs.layers.Convolution2D(32, kernel_size=(5, 5), padding=2, name='Conv2') >>
+     bs.layers.Pooling2D(type='max', kernel_size=(3, 3), stride=(2, 2)) >>
+     bs.layers.Convolution2D(64, kernel_size=(5, 5), padding=2, name='Conv3') >>
+     bs.layers.Pooling2D(type='max', kernel_size=(3, 3), stride=(2, 2)) >>
+     bs.layers.FullyConnected(64, name='FC') >> fc)
+    net = bs.Network.from_layer(fc)
+    net.initialize({'Conv*': {'W': bs.initializers.Gaussian(0.01), 'bias': 0},
+                    'FC': {'W': bs.initializers.Gaussian(0.1), 'bias': 0},
+                    'Output_projection': {'W': bs.initializers.Gaussian(0.1), 'bias': 0}})
+    rs = np.random.RandomState(data_seed)
+    data = {'default': rs.randn(1, batch, 32, 32, 3).astype(np.float32),
+            'targets': rs.randint(0, 10, (1, batch, 1)).astype(np.int32)}
+    stepper = lambda: bs.training.MomentumStepper(learning_rate=0.01, momentum=0.9)
+    return net, data, stepper
+
+
 def train_steps(net, data, stepper, steps):
     """Runs `steps` updates exactly as Trainer does per minibatch
     (training/trainer.py:96-101): provide data, stepper.run, read the loss."""
