@@ -404,8 +404,10 @@ def lstm_training(H, world, rank, steps, barrier, lib):
 
 
 def other_training(name, H, world, rank, barrier, lib, new_event, elapsed):
-    """The two other training workloads.  'mlp': the MNIST-style MLP, batch 100 per GPU
-    (weak scaling), momentum SGD.  'highway_bn': ten Highway + BatchNorm blocks of width
+    """The other training workloads.  'mlp': the MNIST-style MLP, batch 100 per GPU
+    (weak scaling), momentum SGD.  'cifar10_cnn': the convolutional network of the reference's
+    examples/cifar10_cnn.py, batch 100 per GPU, momentum SGD; rank 0 also times two updates of
+    the same network on the reference's NumpyHandler.  'highway_bn': ten Highway + BatchNorm blocks of width
     4096, batch 8192 in total (strong scaling: 8192 / N rows per GPU), BatchNorm statistics
     completed across the shards inside sum_t(axis=0).  Plain stepper and the same step
     replayed from a recording; at N > 1 the Highway step also reports its phases."""
@@ -415,6 +417,9 @@ def other_training(name, H, world, rank, barrier, lib, new_event, elapsed):
     from brainstorm_b200 import GraphedStepper, workloads
     if name == 'mlp':
         net, data, stepper = workloads.mlp(batch=100, data_seed=rank)
+        global_batch, steps, mode = 100 * world, 50, 'local'
+    elif name == 'cifar10_cnn':
+        net, data, stepper = workloads.cifar10_cnn(batch=100, data_seed=rank)
         global_batch, steps, mode = 100 * world, 50, 'local'
     else:
         net, data, stepper = workloads.highway_bn(batch=8192 // world, data_seed=rank)
@@ -490,7 +495,7 @@ def other_training(name, H, world, rank, barrier, lib, new_event, elapsed):
                                'launches_per_step': int((lib.b200_launch_count() - l0) // (steps + 3))}
         ms = _pipelined_ms(net, lambda: st.run(), H, host_data, data['default'].shape[1], steps + 3, 3, barrier, world)
         out['fused_layers']['pipelined_ms_per_step'] = round(ms, 3)
-    if name == 'mlp' or world > 1:
+    if name in ('mlp', 'cifar10_cnn') or world > 1:
         gs = GraphedStepper(stepper(), eager_steps=1)
         gs.start(net)
         st = gs
@@ -504,6 +509,18 @@ def other_training(name, H, world, rank, barrier, lib, new_event, elapsed):
             out['recorded_pipelined_ms_per_step'] = round(ms, 3)
             out['recorded_pipelined_samples_per_s'] = round(global_batch / ms * 1e3, 1)
         gs.invalidate()
+    if name == 'cifar10_cnn' and rank == 0:
+        from brainstorm.handlers import NumpyHandler
+        ref, rdata, rstepper = workloads.cifar10_cnn(batch=100, data_seed=rank)
+        ref.set_handler(NumpyHandler(np.float32))
+        rs_ = rstepper()
+        rs_.start(ref)
+        t0 = time.perf_counter()
+        for _ in range(2):
+            ref.provide_external_data(rdata)
+            rs_.run()
+            float(ref.get_loss_values()['total_loss'])
+        out['numpy_handler_ms_per_step'] = round((time.perf_counter() - t0) / 2 * 1e3, 1)
     return out
 
 
@@ -640,7 +657,7 @@ def run_b200(args):
     if args.only == 'gemms':
         return finish({'metric': 'dot_mm_fp32_tflops', 'n_gpus': world,
                        'gemm': gemm_block(H, lib, check, new_event, elapsed, local_rank, peaks)})
-    if args.only in ('mlp', 'highway_bn'):
+    if args.only in ('mlp', 'highway_bn', 'cifar10_cnn'):
         res = other_training(args.only, H, world, rank, barrier, lib, new_event, elapsed)
         return finish({'metric': '%s_train_samples_per_s' % args.only, 'value': res.get('samples_per_s'),
                        'unit': 'samples/s', 'n_gpus': world, 'detail': res})
@@ -782,7 +799,7 @@ def run_b200(args):
 
     gemm = gemm_block(H, lib, check, new_event, elapsed, local_rank, peaks)
     lstm = lstm_training(H, world, rank, max(3, min(args.steps, 10)), barrier, lib)
-    others = {n: other_training(n, H, world, rank, barrier, lib, new_event, elapsed) for n in ('mlp', 'highway_bn')}
+    others = {n: other_training(n, H, world, rank, barrier, lib, new_event, elapsed) for n in ('mlp', 'cifar10_cnn', 'highway_bn')}
     if comm is not None:
         comm.close()
 
@@ -916,7 +933,7 @@ def main():
     ap.add_argument('--steps', type=int, default=30)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
-    ap.add_argument('--only', default='all', choices=['all', 'suite', 'ops', 'gemm', 'gemms', 'lstm', 'mlp', 'highway_bn'],
+    ap.add_argument('--only', default='all', choices=['all', 'suite', 'ops', 'gemm', 'gemms', 'lstm', 'mlp', 'cifar10_cnn', 'highway_bn'],
                     help='suite: device-resident op suite only; gemm: one dot_mm shape (for profiling); '
                          'gemms: the GEMM block of the bench line')
     ap.add_argument('--rows', type=int, default=ROWS, help='rows of the op-suite operands (default 65536)')
