@@ -6,6 +6,7 @@
 // adds the partials in a fixed order.  No floating-point atomics anywhere, so the
 // same input always gives the same bits.
 #include "common.cuh"
+#include "peer.cuh"
 
 namespace b200 {
 
@@ -71,39 +72,58 @@ sum_all_pass2(const float* partial, int count, float* out) {
 // one set per library stream: calls on one stream are ordered, and the two streams never
 // share a set.
 constexpr int AXIS0_TICKET_SLOTS = 4096;     // column groups per call that can use the folded form
-__device__ unsigned g_axis0_tickets[2][AXIS0_TICKET_SLOTS];
+__device__ unsigned g_axis0_tickets[2][AXIS0_TICKET_SLOTS + 1];   // the last one of a set counts finished column groups
 
-// Called by all 256 threads of a 32 x 8 block after they have stored their partials.
-// `width` columns from `col0` belong to this block.
+// Called by all 256 threads of a 32 x 8 block after they have stored their partials (or, with a
+// single chunk of rows, their sums).  `width` columns from `col0` belong to this block.
+// peer_mode 1 / 2: the sums are then completed across the ranks (sum / mean) by the block that
+// finishes the last column group -- the all-reduce over peer memory of peer.cuh, run inside
+// this kernel instead of as a launch behind it.
 __device__ __forceinline__ void axis0_fold_pass2(unsigned* tickets, const float* partial, const float* partial2, float* out,
-                                                 float* out2, int64_t cols, int64_t col0, int width) {
+                                                 float* out2, int64_t cols, int64_t col0, int width,
+                                                 const PeerArgs& peer, int peer_mode, int* error_flag, unsigned spin_limit) {
   __shared__ int is_last;
+  const int t = threadIdx.y * 32 + threadIdx.x;
+  const int chunks = (int)gridDim.y;
+  if (chunks > 1) {
+    __threadfence();
+    __syncthreads();
+    if (t == 0) {
+      const unsigned drawn = atomicAdd(&tickets[blockIdx.x], 1u);
+      is_last = drawn == gridDim.y - 1;
+      if (is_last) tickets[blockIdx.x] = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int j = t; j < width * (partial2 ? 2 : 1); j += 256) {
+      const float* p = j < width ? partial : partial2;
+      float* o = j < width ? out : out2;
+      const int64_t c = col0 + (j < width ? j : j - width);
+      if (c >= cols) continue;
+      float s0 = 0.f, s1 = 0.f;
+      int k = 0;
+      for (; k + 1 < chunks; k += 2) {
+        s0 += __ldcg(p + (int64_t)k * cols + c);
+        s1 += __ldcg(p + (int64_t)(k + 1) * cols + c);
+      }
+      if (k < chunks) s0 += __ldcg(p + (int64_t)k * cols + c);
+      o[c] = s0 + s1;
+    }
+  }
+  if (peer_mode == 0) return;
+  // one ticket per finished column group; the block that draws the last one holds the exchange
   __threadfence();
   __syncthreads();
-  const int t = threadIdx.y * 32 + threadIdx.x;
   if (t == 0) {
-    const unsigned drawn = atomicAdd(&tickets[blockIdx.x], 1u);
-    is_last = drawn == gridDim.y - 1;
-    if (is_last) tickets[blockIdx.x] = 0;
+    const unsigned drawn = atomicAdd(&tickets[AXIS0_TICKET_SLOTS], 1u);
+    is_last = drawn == gridDim.x - 1;
+    if (is_last) tickets[AXIS0_TICKET_SLOTS] = 0;
   }
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  const int chunks = (int)gridDim.y;
-  for (int j = t; j < width * (partial2 ? 2 : 1); j += 256) {
-    const float* p = j < width ? partial : partial2;
-    float* o = j < width ? out : out2;
-    const int64_t c = col0 + (j < width ? j : j - width);
-    if (c >= cols) continue;
-    float s0 = 0.f, s1 = 0.f;
-    int k = 0;
-    for (; k + 1 < chunks; k += 2) {
-      s0 += __ldcg(p + (int64_t)k * cols + c);
-      s1 += __ldcg(p + (int64_t)(k + 1) * cols + c);
-    }
-    if (k < chunks) s0 += __ldcg(p + (int64_t)k * cols + c);
-    o[c] = s0 + s1;
-  }
+  peer_exchange_block(peer, out, out, (int)cols, peer_mode == 2, error_flag, spin_limit);
 }
 
 // Block = 32 x 8 threads.  VEC: a thread owns 4 adjacent columns (block covers
@@ -112,7 +132,8 @@ __device__ __forceinline__ void axis0_fold_pass2(unsigned* tickets, const float*
 template <bool VEC>
 __global__ void __launch_bounds__(256)
 sum_axis0_pass1(const float* a, int64_t rows, int64_t cols, int64_t ld, int64_t rows_per_chunk,
-                float* dst, float* out, unsigned* tickets) {
+                float* dst, float* out, unsigned* tickets, PeerArgs peer, int peer_mode, int* error_flag,
+                unsigned spin_limit) {
   constexpr int W = VEC ? 4 : 1;
   __shared__ float smem[8][32 * W + 1];
   const int tx = threadIdx.x, ty = threadIdx.y;
@@ -165,7 +186,9 @@ sum_axis0_pass1(const float* a, int64_t rows, int64_t cols, int64_t ld, int64_t 
     const int64_t cc = (int64_t)blockIdx.x * 32 * W + j;
     if (cc < cols) dst[(int64_t)blockIdx.y * cols + cc] = s;
   }
-  if (tickets) axis0_fold_pass2(tickets, dst, nullptr, out, nullptr, cols, (int64_t)blockIdx.x * 32 * W, 32 * W);
+  if (tickets)
+    axis0_fold_pass2(tickets, dst, nullptr, out, nullptr, cols, (int64_t)blockIdx.x * 32 * W, 32 * W, peer, peer_mode,
+                     error_flag, spin_limit);
 }
 
 // ---- column sums with the producing elementwise step folded in (BatchNorm) -------------
@@ -249,7 +272,7 @@ bn_colsum_pass1(const float* a, const float* b, const float* vec, float* centere
   }
   if (tickets)
     axis0_fold_pass2(tickets, dst, MODE == 1 ? dst2 : nullptr, out, MODE == 1 ? out + cols : nullptr, cols,
-                     (int64_t)blockIdx.x * 128, 128);
+                     (int64_t)blockIdx.x * 128, 128, PeerArgs{}, 0, nullptr, 0);
 }
 
 // out[c] = sum over chunks of partial[chunk * cols + c], fixed order
@@ -464,6 +487,42 @@ static int sum_all_contiguous(const float* a, int64_t n, float* out, float* scra
   return B200_OK;
 }
 
+namespace b200 { int* device_error_flag(); }   // gemm_tc.cu: the mapped word that bounded device waits raise
+B200_API int b200_peer_allreduce(const float* src, float* dst, int n, int average);   // peer.cu
+B200_API int b200_peer_enabled(void);
+
+// Column sums.  peer_mode 1 / 2 also completes them across the ranks (sum / mean) over peer memory: inside the
+// kernel when the ticket counters can serve this launch, else by the all-reduce kernel behind it.
+static int sum_axis0(const float* a, int64_t rows, int64_t cols, int64_t ld, float* out, float* scratch, int peer_mode) {
+  const State& s = state();
+  const bool vec = (cols % 4 == 0) && (ld % 4 == 0) && aligned16(a);
+  // the plan must not depend on the pointer: recompute with the layout-only rule
+  const bool vec_layout = (cols % 4 == 0) && (ld % 4 == 0);
+  int64_t rpc;
+  const int chunks = axis0_plan(rows, cols, vec_layout, &rpc);
+  float* dst = chunks > 1 ? scratch : out;
+  const int64_t groups = ceil_div(cols, vec ? 128 : 32);
+  unsigned* tickets = (chunks > 1 || peer_mode) ? axis0_tickets(groups) : nullptr;
+  PeerArgs peer{};
+  const bool fused = peer_mode != 0 && tickets != nullptr && peer_args(&peer);
+  const int mode = fused ? peer_mode : 0;
+  unsigned* use = (chunks > 1 || fused) ? tickets : nullptr;
+  dim3 grid((unsigned)groups, chunks);
+  if (vec)
+    sum_axis0_pass1<true><<<grid, dim3(32, 8), 0, s.stream>>>(a, rows, cols, ld, rpc, dst, out, use, peer, mode,
+                                                              device_error_flag(), s.peer_spin_limit);
+  else
+    sum_axis0_pass1<false><<<grid, dim3(32, 8), 0, s.stream>>>(a, rows, cols, ld, rpc, dst, out, use, peer, mode,
+                                                               device_error_flag(), s.peer_spin_limit);
+  B200_LAUNCH_CHECK();
+  if (chunks > 1 && !use) {
+    sum_axis0_pass2<<<(unsigned)ceil_div(cols, 256), 256, 0, s.stream>>>(scratch, chunks, cols, out);
+    B200_LAUNCH_CHECK();
+  }
+  if (peer_mode != 0 && !fused) return b200_peer_allreduce(out, out, (int)cols, peer_mode == 2);
+  return B200_OK;
+}
+
 // axis: 0 -> out[c] = sum_r a[r, c]; 1 -> out[r] = sum_c a[r, c]; -1 -> out[0] = sum of all.
 B200_API int b200_sum_t(const float* a, int64_t rows, int64_t cols, int64_t ld, int axis, float* out,
                         float* scratch, int64_t scratch_floats) {
@@ -481,29 +540,7 @@ B200_API int b200_sum_t(const float* a, int64_t rows, int64_t cols, int64_t ld, 
   B200_REQUIRE(need == 0 || (scratch != nullptr && scratch_floats >= need),
                "sum_t needs %lld floats of scratch, got %lld", (long long)need,
                (long long)scratch_floats);
-  if (axis == 0) {
-    const bool vec = (cols % 4 == 0) && (ld % 4 == 0) && aligned16(a);
-    // the plan must not depend on the pointer: recompute with the layout-only rule
-    const bool vec_layout = (cols % 4 == 0) && (ld % 4 == 0);
-    int64_t rpc;
-    const int chunks = axis0_plan(rows, cols, vec_layout, &rpc);
-    float* dst = chunks > 1 ? scratch : out;
-    const int64_t groups = ceil_div(cols, vec ? 128 : 32);
-    unsigned* tickets = chunks > 1 ? axis0_tickets(groups) : nullptr;
-    if (vec) {
-      dim3 grid((unsigned)groups, chunks);
-      sum_axis0_pass1<true><<<grid, dim3(32, 8), 0, s.stream>>>(a, rows, cols, ld, rpc, dst, out, tickets);
-    } else {
-      dim3 grid((unsigned)groups, chunks);
-      sum_axis0_pass1<false><<<grid, dim3(32, 8), 0, s.stream>>>(a, rows, cols, ld, rpc, dst, out, tickets);
-    }
-    B200_LAUNCH_CHECK();
-    if (chunks > 1 && !tickets) {
-      sum_axis0_pass2<<<(unsigned)ceil_div(cols, 256), 256, 0, s.stream>>>(scratch, chunks, cols, out);
-      B200_LAUNCH_CHECK();
-    }
-    return B200_OK;
-  }
+  if (axis == 0) return sum_axis0(a, rows, cols, ld, out, scratch, 0);
   if (axis == 1) {
     const bool vec = (cols % 4 == 0) && (ld % 4 == 0) && aligned16(a);
     const unsigned grid = (unsigned)ceil_div(rows, 8);
@@ -518,6 +555,28 @@ B200_API int b200_sum_t(const float* a, int64_t rows, int64_t cols, int64_t ld, 
   sum_axis1_kernel<false><<<(unsigned)ceil_div(rows, 8), 256, 0, s.stream>>>(a, rows, cols, ld, rowsum);
   B200_LAUNCH_CHECK();
   return sum_all_contiguous(rowsum, rows, out, scratch);
+}
+
+// b200_sum_t(axis 0) completed across the ranks of the peer registration (b200_peer_setup): out[c] = sum (average != 0:
+// mean) over ranks of the local column sums, the same bits on every rank.  One kernel: the block that finishes the
+// last column group runs the exchange of b200_peer_allreduce (same protocol, same bounded wait, same error reporting;
+// after a wait that ran out `out` holds the local sums).  cols <= b200_peer_max_floats(); every rank makes the call.
+B200_API int b200_sum_t_axis0_allreduce(const float* a, int64_t rows, int64_t cols, int64_t ld, float* out, float* scratch,
+                                        int64_t scratch_floats, int average) {
+  if (int rc = require_ready()) return rc;
+  B200_REQUIRE(rows >= 0 && cols >= 0 && out != nullptr, "bad extent or NULL out");
+  B200_REQUIRE(cols <= PEER_MAX_FLOATS, "at most %d columns", PEER_MAX_FLOATS);
+  B200_REQUIRE(b200_peer_enabled(), "no usable peer registration (b200_peer_setup)");
+  if (cols == 0) return B200_OK;
+  if (rows == 0) {
+    B200_CUDA(cudaMemsetAsync(out, 0, cols * sizeof(float), state().stream));
+    return b200_peer_allreduce(out, out, (int)cols, average);
+  }
+  B200_REQUIRE(a != nullptr && ld >= cols, "bad operand");
+  const int64_t need = b200_sum_t_scratch_floats(rows, cols, ld, 0);
+  B200_REQUIRE(need == 0 || (scratch != nullptr && scratch_floats >= need), "sum_t needs %lld floats of scratch, got %lld",
+               (long long)need, (long long)scratch_floats);
+  return sum_axis0(a, rows, cols, ld, out, scratch, average ? 2 : 1);
 }
 
 B200_API int b200_softmax_m(const float* m, float* out, int64_t rows, int64_t cols, int64_t ldm,
@@ -673,7 +732,7 @@ unsigned* axis0_tickets(int64_t groups) {
   const State& s = state();
   if (!s.axis0_fold || groups > AXIS0_TICKET_SLOTS || s.device < 0 || s.device >= 64) return nullptr;
   unsigned* base = g_axis0_tickets_ptr[s.device];
-  return base ? base + (s.stream_index ? AXIS0_TICKET_SLOTS : 0) : nullptr;
+  return base ? base + (s.stream_index ? AXIS0_TICKET_SLOTS + 1 : 0) : nullptr;
 }
 }  // namespace b200
 

@@ -528,10 +528,18 @@ class B200Handler(Handler):
         dst = out if out._contig else B200Array.empty((nout,), zero=False)
         need = lib.b200_sum_t_scratch_floats(rows, cols, ld, ax)
         sp, sn = self._scratch_for(need)
-        check(lib.b200_sum_t(a.ptr, rows, cols, ld, ax, dst.ptr, sp, sn))
+        exchange = False
         if ax == 0 and self._comm is not None and self.axis0_reduce != 'local':
             lo, hi = self._axis0_skip
-            if not (lo <= out.ptr < hi):        # sums written into the gradient vector are averaged with it
+            exchange = not (lo <= out.ptr < hi)     # sums written into the gradient vector are averaged with it
+        peer_ok = getattr(self._comm, '_peer_ok', None) if exchange else None
+        if peer_ok is not None and peer_ok(dst):
+            # sum and exchange as one kernel: its last block completes the sums across the ranks over peer memory
+            check(lib.b200_sum_t_axis0_allreduce(a.ptr, rows, cols, ld, dst.ptr, sp, sn,
+                                                 1 if self.axis0_reduce == 'avg' else 0))
+        else:
+            check(lib.b200_sum_t(a.ptr, rows, cols, ld, ax, dst.ptr, sp, sn))
+            if exchange:
                 self._allreduce_axis0(dst)
         if dst is not out:
             self.copy_to(dst.reshape(out.shape), out)

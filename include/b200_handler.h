@@ -154,6 +154,15 @@ int b200_peer_setup(int rank, int world, const uint64_t* windows);
 int b200_peer_enabled(void);
 int b200_peer_allreduce(const float* src, float* dst, int n, int average);
 int b200_peer_wait_stats(uint64_t* calls, uint64_t* waited_ns);
+/* b200_sum_t(axis 0) and b200_peer_allreduce of its result as ONE kernel: the block of
+ * the column-sum kernel that finishes last runs the exchange (same protocol, bounded wait
+ * and error reporting as b200_peer_allreduce; after a wait that ran out, out holds the
+ * local sums).  out[c] = sum (average != 0: mean) over the ranks of the local column
+ * sums, the same bits on every rank and the same bits as the two calls.  cols <=
+ * b200_peer_max_floats(); scratch as for b200_sum_t(axis 0); every rank makes the call.
+ * Serves sum_t(axis=0) of batch-sharded data (BatchNorm statistics,
+ * batch_normalization_layer.py:63,83,121,133). */
+int b200_sum_t_axis0_allreduce(const float* a, int64_t rows, int64_t cols, int64_t ld, float* out, float* scratch, int64_t scratch_floats, int average);
 int b200_peer_teardown(void);
 
 /* ---- all-reduce of device arrays over NCCL -----------------------------------

@@ -52,6 +52,33 @@ def main():
                         if rank == 0:
                             print('peer all-reduce n=%d %s: replicas equal %s, max diff to NCCL %.3g' % (
                                 n, op, same, np.abs(got - want).max()))
+        # the column sum with the exchange inside its kernel against the sum followed by NCCL
+        for rows, cols in ((4096, 4096), (300, 1027), (64, 8), (20000, 512)):
+            x = np.random.RandomState(7 * rank + rows).randn(rows, cols).astype(np.float32)
+            a = H.create_from_numpy(x)
+            for op in ('sum', 'avg'):
+                want, got = H.zeros((1, cols)), H.zeros((1, cols))
+                H.sum_t(a, 0, want)
+                plain.allreduce(want, op)
+                two_calls = H.zeros((1, cols))
+                H.sum_t(a, 0, two_calls)
+                peer.allreduce(two_calls, op)
+                H.set_comm(peer, op)
+                H.sum_t(a, 0, got)
+                H.set_comm(None, 'local')
+                g, w = H.get_numpy_copy(got), H.get_numpy_copy(want)
+                if not np.array_equal(g, H.get_numpy_copy(two_calls)):
+                    ok = False
+                    print('fused column sum (%d, %d) %s: bits differ from sum_t + peer all-reduce on rank %d' % (rows, cols, op, rank))
+                gathered = [None] * world
+                dist.all_gather_object(gathered, g)
+                same = all(np.array_equal(v, gathered[0]) for v in gathered)
+                close = np.allclose(g, w, rtol=1e-6, atol=1e-5 * np.abs(x).sum(0).max())
+                if not (same and close):
+                    ok = False
+                    if rank == 0:
+                        print('fused column sum (%d, %d) %s: replicas equal %s, max diff to NCCL %.3g' % (
+                            rows, cols, op, same, np.abs(g - w).max()))
         peer.close()
     for which, build, mode in (
             ('highway_bn', lambda: workloads.highway_bn(batch=32 * world, width=64, classes=7, blocks=2), 'avg'),

@@ -75,3 +75,74 @@ def test_a_rank_that_never_arrives_makes_the_wait_run_out_and_is_reported():
         lib.b200_sync()
         check(lib.b200_peer_teardown())               # frees window 0 (this rank's)
         check(lib.b200_peer_window_release(wins[1].value, 1))
+
+
+def _sum0_fused(H, lib, check, x, average):
+    a = H.create_from_numpy(x)
+    out = H.create_from_numpy(np.full((x.shape[1],), np.nan, np.float32))
+    sp, sn = H._scratch_for(lib.b200_sum_t_scratch_floats(x.shape[0], x.shape[1], x.shape[1], 0))
+    check(lib.b200_sum_t_axis0_allreduce(a.ptr, x.shape[0], x.shape[1], x.shape[1], out.ptr, sp, sn, average))
+    return out
+
+
+@pytest.mark.parametrize('rows,cols', [(8, 4), (64, 33), (5000, 128), (4096, 4096), (300, 1027), (70000, 12)])
+def test_column_sum_with_the_exchange_inside_the_kernel_single_rank(rows, cols):
+    """With one rank the completed sums are the local ones: the kernel's second ticket level,
+    the hand-over to the exchange and the counters' return to zero, call after call."""
+    from brainstorm_b200 import B200Handler
+    from brainstorm_b200._lib import lib, check
+    H = B200Handler(seed=1)
+    handle = ctypes.create_string_buffer(64)
+    window = ctypes.c_uint64()
+    check(lib.b200_peer_window_alloc(ctypes.byref(window), handle))
+    check(lib.b200_peer_setup(0, 1, (ctypes.c_uint64 * 1)(window.value)))
+    try:
+        x = np.random.RandomState(rows + cols).randn(rows, cols).astype(np.float32)
+        a, want = H.create_from_numpy(x), H.zeros((1, cols))
+        H.sum_t(a, 0, want)
+        want = H.get_numpy_copy(want).ravel()
+        for call in range(4):
+            got = H.get_numpy_copy(_sum0_fused(H, lib, check, x, call % 2))
+            assert np.array_equal(got, want), 'call %d' % call
+        calls, waited = ctypes.c_uint64(), ctypes.c_uint64()
+        check(lib.b200_peer_wait_stats(ctypes.byref(calls), ctypes.byref(waited)))
+        assert calls.value == 4
+    finally:
+        H.synchronize()
+        check(lib.b200_peer_teardown())
+
+
+def test_column_sum_whose_exchange_gives_up_keeps_the_local_sums():
+    """The fused form of the failure path above: "rank 1" never arrives, the wait inside the
+    column-sum kernel runs out after a few milliseconds, the kernel returns, `out` holds the
+    local sums, the error is reported at the next synchronising call and the path is off."""
+    from brainstorm_b200 import B200Handler, B200Error
+    from brainstorm_b200._lib import lib, check
+    H = B200Handler(seed=1)
+    handles = [ctypes.create_string_buffer(64) for _ in range(2)]
+    wins = [ctypes.c_uint64() for _ in range(2)]
+    for w, h in zip(wins, handles):
+        check(lib.b200_peer_window_alloc(ctypes.byref(w), h))
+    check(lib.b200_peer_setup(0, 2, (ctypes.c_uint64 * 2)(wins[0].value, wins[1].value)))
+    check(lib.b200_set_tuning(8, 12))                 # 2^12 polls: about 12 ms
+    try:
+        x = np.random.RandomState(5).randn(3000, 256).astype(np.float32)
+        a, want = H.create_from_numpy(x), H.zeros((1, 256))
+        H.sum_t(a, 0, want)
+        want = H.get_numpy_copy(want).ravel()
+        out = _sum0_fused(H, lib, check, x, 0)        # queued; rank 1 never comes
+        with pytest.raises(B200Error, match='gave up waiting'):
+            H.synchronize()
+        assert lib.b200_peer_enabled() == 0
+        assert np.array_equal(H.get_numpy_copy(out), want)
+        sp, sn = H._scratch_for(lib.b200_sum_t_scratch_floats(3000, 256, 256, 0))
+        assert lib.b200_sum_t_axis0_allreduce(a.ptr, 3000, 256, 256, out.ptr, sp, sn, 0) != 0
+        assert b'no usable peer registration' in lib.b200_last_error()
+        got = H.zeros((1, 256))
+        H.sum_t(a, 0, got)                            # ordinary column sums still work: the tickets are back at zero
+        assert np.array_equal(H.get_numpy_copy(got).ravel(), want)
+    finally:
+        check(lib.b200_set_tuning(8, 0))
+        lib.b200_sync()
+        check(lib.b200_peer_teardown())
+        check(lib.b200_peer_window_release(wins[1].value, 1))
