@@ -64,6 +64,8 @@ struct State {
   int ew_blocks_per_sm = 32;
   int ew_threads = 1024;
   int red_blocks_per_sm = 8;   // pass-1 blocks per SM of the two-pass sums
+  int axis0_peer_fused = 0;    // b200_sum_t_axis0_allreduce: 1 = the exchange runs inside the column-sum kernel, group by group
+                               // (measured slower than the all-reduce kernel behind it, which is the default)
   int axis0_fold = 1;          // column sums: the last pass-1 block of a column group does pass 2 (0: a launch of its own)
   int gemm_path = 0;  // 0 = auto, 1 = force SIMT, 2 = force tensor-core
   int gemm_bn = 0;    // 0 = auto, else forced tile width (32/64/128/256)

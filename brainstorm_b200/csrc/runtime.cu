@@ -137,6 +137,7 @@ B200_API int b200_set_tuning(int key, int value) {
     case 6: B200_REQUIRE(value >= 1 && value <= 8, "SM share divisor out of range"); s.sm_share = value; break;
     case 10: B200_REQUIRE(value >= 1 && value <= 27, "reduction blocks per SM out of range"); s.red_blocks_per_sm = value; break;
     case 11: B200_REQUIRE(value == 0 || value == 1, "axis-0 fold is 0 or 1"); s.axis0_fold = value; break;
+    case 12: B200_REQUIRE(value == 0 || value == 1, "in-kernel exchange is 0 or 1"); s.axis0_peer_fused = value; break;
     case 9: B200_REQUIRE(value == 0 || value == 1 || value == 2 || value == 4 || value == 8, "chunk must be 0, 1, 2, 4 or 8 k-blocks");
             s.gemm_chunk_kb = value; break;
     case 8: B200_REQUIRE(value >= 0 && value <= 30, "spin limit exponent out of range (0 = default)");

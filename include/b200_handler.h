@@ -52,7 +52,10 @@ int b200_device_info(int* device, int* sm_count, uint64_t* free_bytes, uint64_t*
  *    b200_sum_t_scratch_floats returns);
  * 11: column sums (axis 0) run their second pass inside the first kernel: the block that
  *    finishes a column group last adds the group's partial sums, in the same fixed order
- *    (default 1; 0 = a second launch; same bits either way). */
+ *    (default 1; 0 = a second launch; same bits either way);
+ * 12: b200_sum_t_axis0_allreduce runs its exchange inside the column-sum kernel, group by
+ *    group (1), or as the all-reduce kernel behind it (0, the default: measured faster);
+ *    same bits either way. */
 int b200_set_tuning(int key, int value);
 uint64_t b200_stream(void);                            /* the main stream (a cudaStream_t) */
 /* A second compute stream, for work that may run beside the main stream's (a stack of
@@ -154,10 +157,13 @@ int b200_peer_setup(int rank, int world, const uint64_t* windows);
 int b200_peer_enabled(void);
 int b200_peer_allreduce(const float* src, float* dst, int n, int average);
 int b200_peer_wait_stats(uint64_t* calls, uint64_t* waited_ns);
-/* b200_sum_t(axis 0) and b200_peer_allreduce of its result as ONE kernel: the block of
- * the column-sum kernel that finishes last runs the exchange (same protocol, bounded wait
- * and error reporting as b200_peer_allreduce; after a wait that ran out, out holds the
- * local sums).  out[c] = sum (average != 0: mean) over the ranks of the local column
+/* b200_sum_t(axis 0) and b200_peer_allreduce of its result in one call.  By default the
+ * all-reduce kernel is queued behind the column-sum kernel.  With b200_set_tuning(12, 1)
+ * it is ONE kernel: the block of the column-sum kernel that finishes a group of 128
+ * columns sends that group through the exchange at once, while other groups are still
+ * being summed (same slots, bounded wait and error reporting as b200_peer_allreduce;
+ * after a wait that ran out, out holds the local sums); on two B200s that form measured
+ * 200 us against 191 us for the two kernels on a (65536, 4096) array.  out[c] = sum (average != 0: mean) over the ranks of the local column
  * sums, the same bits on every rank and the same bits as the two calls.  cols <=
  * b200_peer_max_floats(); scratch as for b200_sum_t(axis 0); every rank makes the call.
  * Serves sum_t(axis=0) of batch-sharded data (BatchNorm statistics,

@@ -26,6 +26,7 @@ def main():
     from brainstorm_b200 import parallel
     from brainstorm_b200.parallel import Comm, data_parallel, shard_batch
     from brainstorm_b200.workloads import train_steps
+    from brainstorm_b200._lib import lib, check
     H = B200Handler(seed=3, device=local)
     ok = True
     # ---- the library's all-reduce over peer memory against NCCL, op by op
@@ -56,7 +57,8 @@ def main():
         for rows, cols in ((4096, 4096), (300, 1027), (64, 8), (20000, 512)):
             x = np.random.RandomState(7 * rank + rows).randn(rows, cols).astype(np.float32)
             a = H.create_from_numpy(x)
-            for op in ('sum', 'avg'):
+            for op, in_kernel in (('sum', 1), ('avg', 1), ('sum', 0), ('avg', 0)):
+                check(lib.b200_set_tuning(12, in_kernel))
                 want, got = H.zeros((1, cols)), H.zeros((1, cols))
                 H.sum_t(a, 0, want)
                 plain.allreduce(want, op)
@@ -79,6 +81,7 @@ def main():
                     if rank == 0:
                         print('fused column sum (%d, %d) %s: replicas equal %s, max diff to NCCL %.3g' % (
                             rows, cols, op, same, np.abs(g - w).max()))
+        check(lib.b200_set_tuning(12, 0))
         peer.close()
     for which, build, mode in (
             ('highway_bn', lambda: workloads.highway_bn(batch=32 * world, width=64, classes=7, blocks=2), 'avg'),

@@ -64,7 +64,7 @@ def test_scratch_size_query_needs_no_device():
 def test_peer_allreduce_entry_points_refuse_to_run_unconfigured():
     """No GPU here: the peer all-reduce must say what is missing instead of crashing."""
     from brainstorm_b200._lib import lib
-    assert lib.b200_peer_window_bytes() == 2 * 65536 * 4 + 256
+    assert lib.b200_peer_window_bytes() == 2 * 65536 * 4 + 256 + 16 * 512 * 8    # two slots, the counters, the per-group counters
     assert lib.b200_peer_max_floats() == 65536
     assert lib.b200_peer_allreduce(None, None, 4, 0) != 0
     assert lib.b200_peer_teardown() == 0          # nothing set up: nothing to do

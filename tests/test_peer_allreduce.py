@@ -77,7 +77,8 @@ def test_a_rank_that_never_arrives_makes_the_wait_run_out_and_is_reported():
         check(lib.b200_peer_window_release(wins[1].value, 1))
 
 
-def _sum0_fused(H, lib, check, x, average):
+def _sum0_fused(H, lib, check, x, average, in_kernel=1):
+    check(lib.b200_set_tuning(12, in_kernel))       # 1: the exchange inside the column-sum kernel; 0: the kernel behind it
     a = H.create_from_numpy(x)
     out = H.create_from_numpy(np.full((x.shape[1],), np.nan, np.float32))
     sp, sn = H._scratch_for(lib.b200_sum_t_scratch_floats(x.shape[0], x.shape[1], x.shape[1], 0))
@@ -101,13 +102,14 @@ def test_column_sum_with_the_exchange_inside_the_kernel_single_rank(rows, cols):
         a, want = H.create_from_numpy(x), H.zeros((1, cols))
         H.sum_t(a, 0, want)
         want = H.get_numpy_copy(want).ravel()
-        for call in range(4):
-            got = H.get_numpy_copy(_sum0_fused(H, lib, check, x, call % 2))
+        for call in range(6):                      # both forms, interleaved: they share slots and call numbers
+            got = H.get_numpy_copy(_sum0_fused(H, lib, check, x, call % 2, in_kernel=1 if call % 3 else 0))
             assert np.array_equal(got, want), 'call %d' % call
         calls, waited = ctypes.c_uint64(), ctypes.c_uint64()
         check(lib.b200_peer_wait_stats(ctypes.byref(calls), ctypes.byref(waited)))
-        assert calls.value == 4
+        assert calls.value == 6
     finally:
+        check(lib.b200_set_tuning(12, 0))
         H.synchronize()
         check(lib.b200_peer_teardown())
 
@@ -143,6 +145,7 @@ def test_column_sum_whose_exchange_gives_up_keeps_the_local_sums():
         assert np.array_equal(H.get_numpy_copy(got).ravel(), want)
     finally:
         check(lib.b200_set_tuning(8, 0))
+        check(lib.b200_set_tuning(12, 0))
         lib.b200_sync()
         check(lib.b200_peer_teardown())
         check(lib.b200_peer_window_release(wins[1].value, 1))
