@@ -403,7 +403,7 @@ def lstm_training(H, world, rank, steps, barrier, lib):
     return out
 
 
-def other_training(name, H, world, rank, barrier, lib, new_event, elapsed):
+def other_training(name, H, world, rank, barrier, lib, new_event, elapsed, blocks=10):
     """The other training workloads.  'mlp': the MNIST-style MLP, batch 100 per GPU
     (weak scaling), momentum SGD.  'cifar10_cnn': the convolutional network of the reference's
     examples/cifar10_cnn.py, batch 100 per GPU, momentum SGD; rank 0 also times two updates of
@@ -422,7 +422,7 @@ def other_training(name, H, world, rank, barrier, lib, new_event, elapsed):
         net, data, stepper = workloads.cifar10_cnn(batch=100, data_seed=rank)
         global_batch, steps, mode = 100 * world, 50, 'local'
     else:
-        net, data, stepper = workloads.highway_bn(batch=8192 // world, data_seed=rank)
+        net, data, stepper = workloads.highway_bn(batch=8192 // world, blocks=blocks, data_seed=rank)
         global_batch, steps, mode = 8192, 3 if world == 1 else 6, 'avg'
     pinned = {}
     for k, v in data.items():                     # host batches live in page-locked memory, as in lstm_training
@@ -658,7 +658,7 @@ def run_b200(args):
         return finish({'metric': 'dot_mm_fp32_tflops', 'n_gpus': world,
                        'gemm': gemm_block(H, lib, check, new_event, elapsed, local_rank, peaks)})
     if args.only in ('mlp', 'highway_bn', 'cifar10_cnn'):
-        res = other_training(args.only, H, world, rank, barrier, lib, new_event, elapsed)
+        res = other_training(args.only, H, world, rank, barrier, lib, new_event, elapsed, blocks=args.blocks)
         return finish({'metric': '%s_train_samples_per_s' % args.only, 'value': res.get('samples_per_s'),
                        'unit': 'samples/s', 'n_gpus': world, 'detail': res})
     if args.only == 'lstm':
@@ -939,6 +939,7 @@ def main():
     ap.add_argument('--rows', type=int, default=ROWS, help='rows of the op-suite operands (default 65536)')
     ap.add_argument('--gemm', default='8192,4096,4096', help='M,N,K for --only gemm')
     ap.add_argument('--ops', default='add_tt', help='comma-separated op names for --only ops')
+    ap.add_argument('--blocks', type=int, default=10, help='Highway + BatchNorm blocks for --only highway_bn (profiler captures use 1)')
     args = ap.parse_args()
     if args.impl == 'reference':
         run_reference(args)

@@ -438,6 +438,7 @@ bias_act_vec(float* out, const float* bias, int64_t rows, int cols4, int64_t ld,
 template <class F, bool STREAM>
 __global__ void __launch_bounds__(1024)
 bias_act_flat(float* out, const float* bias, int64_t nvec, int cols4, Params p) {
+  const bool narrow = nvec < ((int64_t)1 << 31);      // 64-bit division only when it has to be
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t base = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; base < nvec; base += stride * EW_UNROLL) {
     float4 a[EW_UNROLL];
@@ -451,7 +452,7 @@ bias_act_flat(float* out, const float* bias, int64_t nvec, int cols4, Params p) 
     for (int u = 0; u < EW_UNROLL; ++u) {
       const int64_t i = base + u * stride;
       if (i >= nvec) continue;
-      const float4 b = *reinterpret_cast<const float4*>(bias + 4 * (i % cols4));
+      const float4 b = *reinterpret_cast<const float4*>(bias + 4 * (narrow ? (int64_t)((unsigned)i % (unsigned)cols4) : i % cols4));
       float4 v;
       v.x = F::apply(__fadd_rn(a[u].x, b.x), 0.f, 0.f, p);
       v.y = F::apply(__fadd_rn(a[u].y, b.y), 0.f, 0.f, p);

@@ -62,9 +62,10 @@ highway_bwd_kernel(const float4* x, const float4* H, const float4* T, const floa
 __global__ void __launch_bounds__(FL_THREADS)
 bn_normalize_kernel(const float4* centered, const float4* sigma, const float4* gamma, const float4* beta, float4* x_hat,
                     float4* out, int64_t nvec, int cols4) {
+  const bool narrow = nvec < ((int64_t)1 << 31);
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
-    const int c = (int)(i % cols4);
+    const int c = narrow ? (int)((unsigned)i % (unsigned)cols4) : (int)(i % cols4);   // 64-bit division only when it has to be
     const float4 v = centered[i], s = sigma[c], g = gamma[c], b = beta[c];
     float4 xh, o;
     FL_EACH4(xh, __fdiv_rn(v.x, s.x), __fdiv_rn(v.y, s.y), __fdiv_rn(v.z, s.z), __fdiv_rn(v.w, s.w));
@@ -80,9 +81,10 @@ bn_normalize_kernel(const float4* centered, const float4* sigma, const float4* g
 __global__ void __launch_bounds__(FL_THREADS)
 bn_deltas_kernel(const float4* dout, const float4* x_hat, const float4* g, const float4* b, const float4* coeff,
                  float4* in_deltas, int64_t nvec, int cols4) {
+  const bool narrow = nvec < ((int64_t)1 << 31);
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
-    const int c = (int)(i % cols4);
+    const int c = narrow ? (int)((unsigned)i % (unsigned)cols4) : (int)(i % cols4);   // 64-bit division only when it has to be
     const float4 d = dout[i], xh = x_hat[i], gg = g[c], bb = b[c], cf = coeff[c];
     float4 acc = in_deltas[i];
 #define BN_D(k) acc.k = __fadd_rn(__fmul_rn(__fsub_rn(__fsub_rn(d.k, __fmul_rn(xh.k, gg.k)), bb.k), cf.k), acc.k);
