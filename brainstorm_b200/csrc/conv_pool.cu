@@ -55,6 +55,34 @@ __global__ void __launch_bounds__(256) im2col_kernel(const float* __restrict__ i
   }
 }
 
+// The same for channel counts that rule out 128-bit accesses (an RGB input layer): one thread per
+// (output position, kernel row) copies the kw * C floats of that kernel row, which are contiguous
+// in the image and in the patch matrix, so the index arithmetic is paid once per kernel row
+// instead of once per float, and a warp still writes one contiguous stretch of the matrix.
+template <typename I>
+__global__ void __launch_bounds__(256) im2col_rows_kernel(const float* __restrict__ in, float* __restrict__ col, Geo g) {
+  const int run = g.kw * g.C;
+  const I total = (I)g.N * g.oh * g.ow * g.kh;
+  for (I i = (I)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (I)gridDim.x * blockDim.x) {
+    const I row = i / g.kh;
+    const int ky = (int)(i - row * g.kh);
+    const int ox = (int)(row % g.ow);
+    const I t = row / g.ow;
+    const int oy = (int)(t % g.oh), n = (int)(t / g.oh);
+    const int y = oy * g.sy - g.pad + ky, x0 = ox * g.sx - g.pad;
+    float* dst = col + i * run;
+    if (y < 0 || y >= g.H) {
+      for (int j = 0; j < run; ++j) dst[j] = 0.f;
+      continue;
+    }
+    const float* src = in + (((I)n * g.H + y) * g.W + x0) * g.C;      // x0 may be negative: guarded below
+    for (int kx = 0; kx < g.kw; ++kx) {
+      const bool inside = x0 + kx >= 0 && x0 + kx < g.W;
+      for (int c = 0; c < g.C; ++c) dst[kx * g.C + c] = inside ? src[kx * g.C + c] : 0.f;
+    }
+  }
+}
+
 // in_deltas[n, y, x, c] += sum over the windows (oy, ox, ky, kx) that cover (y, x)
 template <typename I, int V>
 __global__ void __launch_bounds__(256) col2im_add_kernel(const float* __restrict__ col, float* in_deltas, Geo g) {
@@ -237,7 +265,16 @@ B200_API int b200_im2col(const float* inputs, float* col, int N, int H, int W, i
   if (int rc = check_geo(g)) return rc;
   const int64_t total = (int64_t)N * oh * ow * kh * kw * C;
   if (total == 0) return B200_OK;
-  CONV_POOL_LAUNCH(im2col_kernel, total, total + (int64_t)N * H * W * C, vec4_ok(C, inputs, col), inputs, col, g);
+  if (!vec4_ok(C, inputs, col)) {
+    const int64_t work = (int64_t)N * oh * ow * kh;
+    if (total + (int64_t)N * H * W * C < ((int64_t)1 << 31) - ((int64_t)state().sm_count * 32 * 256))
+      im2col_rows_kernel<int><<<grid_for(work), 256, 0, state().stream>>>(inputs, col, g);
+    else
+      im2col_rows_kernel<int64_t><<<grid_for(work), 256, 0, state().stream>>>(inputs, col, g);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+  }
+  CONV_POOL_LAUNCH(im2col_kernel, total, total + (int64_t)N * H * W * C, true, inputs, col, g);
   B200_LAUNCH_CHECK();
   return B200_OK;
 }
