@@ -39,7 +39,10 @@ def test_fuse_layers_swaps_classes_and_keeps_the_layout():
                                               FusedFullyConnectedLayerImpl)
     net, data, stepper = workloads.highway_bn(batch=8, width=8, classes=3, blocks=2)
     before = {n: (l.parameter_shapes, l.internal_shapes, l.out_shapes) for n, l in net.layers.items()}
+    from brainstorm.describable import get_description
+    described = get_description(net)
     names = fuse_layers(net)
+    assert get_description(net) == described       # a saved network does not tell which classes ran it
     assert sorted(names) == sorted(n for n in net.layers if n[0] in 'HTB' or n == 'Output_projection')
     kinds = {type(l) for l in net.layers.values()}
     assert {FusedHighwayLayerImpl, FusedBatchNormLayerImpl, FusedFullyConnectedLayerImpl} <= kinds

@@ -76,7 +76,7 @@ def test_axis0_sum_is_completed_across_ranks(tmp_path):
 # ---------------------------------------------------------------- network level
 def _build(which):
     from brainstorm_b200 import workloads
-    if which == 'highway_bn':
+    if which in ('highway_bn', 'highway_bn_fused_classes'):
         return workloads.highway_bn(batch=24, width=12, classes=5, blocks=2)
     if which == 'lstm':
         return workloads.lstm(time=4, batch=8, vocab=9, hidden=10)
@@ -97,7 +97,14 @@ def _rank_train(rank, port, which, out_dir, per_layer=True):
 
     net, data, stepper = _build(which)
     net.set_handler(ShardedNumpyHandler(np.float64))
-    data_parallel(net, Comm(), axis0_reduce='avg' if which == 'highway_bn' else 'local')
+    if which == 'highway_bn_fused_classes':
+        # the fused layer classes and stepper on a handler that is not theirs: they run the reference's own chains,
+        # whose column sums the mixin completes across the shards
+        from brainstorm_b200.fused_layers import fuse_layers
+        from brainstorm_b200.steppers import FusedSgdStepper
+        assert len(fuse_layers(net)) == 9
+        stepper = lambda: FusedSgdStepper(learning_rate=0.01)
+    data_parallel(net, Comm(), axis0_reduce='avg' if which.startswith('highway_bn') else 'local')
     losses = train_steps(net, shard_batch(data, rank, WORLD), stepper(), 3)
     np.savez(os.path.join(out_dir, 'r%d.npz' % rank), p=net.get('parameters'),
              g=net.get('gradients'), losses=np.array(losses))
@@ -106,7 +113,7 @@ def _rank_train(rank, port, which, out_dir, per_layer=True):
 
 @needs_reference
 @pytest.mark.parametrize('per_layer', [True, False], ids=['per-layer', 'one-piece'])
-@pytest.mark.parametrize('which', ['lstm', 'highway_bn'])
+@pytest.mark.parametrize('which', ['lstm', 'highway_bn', 'highway_bn_fused_classes'])
 def test_sharded_training_equals_global_batch(tmp_path, which, per_layer):
     from brainstorm.handlers import NumpyHandler
     from brainstorm_b200.workloads import train_steps
